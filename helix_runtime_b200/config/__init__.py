@@ -1,5 +1,6 @@
 from .errors import ConfigError
 from .llama import LlamaConfig
+from .medolorn import MedolornConfig
 from .rekasun import RekasunConfig
 from .zuzadra import ZuzadraConfig
 from .registry import (Architecture, architecture_for, known_architectures, load_config,
@@ -7,7 +8,7 @@ from .registry import (Architecture, architecture_for, known_architectures, load
 from .spec import BlockSpec, ModelSpec, PartSpec, ScheduleEntry
 
 __all__ = [
-    "Architecture", "BlockSpec", "ConfigError", "LlamaConfig", "ModelSpec", "PartSpec", "RekasunConfig",
+    "Architecture", "BlockSpec", "ConfigError", "LlamaConfig", "MedolornConfig", "ModelSpec", "PartSpec", "RekasunConfig",
     "ZuzadraConfig",
     "ScheduleEntry", "architecture_for", "known_architectures", "load_config",
     "read_config_json", "register_architecture",

@@ -65,12 +65,15 @@ class ScheduleEntry:
     entry owns its cache.  ``add_embedding``: before this entry runs, the embedding's output
     (the residual stream as it stood before the first entry) is added to the residual stream
     once more; models that run a stretch of layers several times feed the input back in at
-    the start of every repeat.
+    the start of every repeat.  ``before``: a part of the family ``entry`` that is run before
+    the entry's block on the residual stream and the embedding's output (a model that feeds its
+    input back in through a matrix at the start of every repeat names it here).
     """
 
     block: int
     cache_from: Optional[int] = None
     add_embedding: bool = False
+    before: Optional[PartSpec] = None
 
 
 @dataclasses.dataclass(frozen=True)

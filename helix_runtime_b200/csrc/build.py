@@ -27,6 +27,9 @@ SOURCES = (
     "hx_streams.cu",
     "hx_recurrent.cu",
     "hx_rotary_norm.cu",
+    "hx_gated_connection.cu",
+    "hx_routed_experts.cu",
+    "hx_latent.cu",
     "hx_gemm_simt.cu",
     "hx_gemm_tc.cu",
     "hx_attention.cu",

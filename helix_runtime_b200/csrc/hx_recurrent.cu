@@ -491,6 +491,247 @@ void outer_product_scan_kernel(const OuterScanArgs<T> a) {
   }
 }
 
+// ------------------------------------------------- linear attention with a matrix state
+
+// One [dim x vdim] matrix S per head, walked token by token, in two rules:
+//   plain decay:  S <- g S + k v',                          o = S' q
+//   delta rule:   S <- g S;  u = beta (v - S' k);  S <- S + k u';  o = S' q
+// (the read-out sees the token's own write).  g is a constant of the head, or
+// g = exp(-exp(A_h) softplus(a + bias_h)) from a projected column a; beta = sigmoid(b) from a
+// projected column b.  Queries and keys arrive as projected (or filtered) rows and are made
+// ready in float32 while a tile is staged: either turned into unit vectors per head
+// (x / sqrt(sum x^2 + eps)) or rotated by their position over their first `rotary_dim`
+// coordinates, then scaled by a constant each.  Several value heads may read one query/key
+// head (head h reads h / (heads / qk_heads)).
+template <typename T>
+struct LinearStateArgs {
+  const T* q;
+  const T* k;
+  const T* v;
+  int ld_q, ld_k, ld_v;
+  const T* decay_in;        // [tokens, ld_gates], column = head; null: the head's constant
+  const T* beta_in;         // [tokens, ld_gates], column = head; null with the plain rule
+  int ld_gates;
+  const float* a_log;       // [heads]
+  const float* dt_bias;     // [heads]
+  const float* fixed_decay;     // [heads]: g, and
+  const float* fixed_decay_m1;  // g - 1 rounded from double
+  const int* positions;     // [tokens]; null: no rotation
+  const float* freq;        // [rotary_dim / 2]
+  const double* freq_exact; // the same in double (float32 engine)
+  int rotary_dim, rotary_layout;   // layout 0: pairs (2i, 2i+1); 1: pairs (i, i + rotary_dim/2)
+  int unit_norm;
+  float unit_eps, q_scale, k_scale;
+  float* state;
+  long long state_stride;
+  int head_stride;
+  float* o;                 // [tokens, heads * vdim]
+  const int* request_start;
+  const int* request_slot;
+  int heads, qk_heads, dim, vdim;
+  int parts, block_lanes, tile, per_token;
+};
+
+template <typename T, bool DELTA, bool ONE_TOKEN>
+__global__ __launch_bounds__(SCAN_THREADS, ONE_TOKEN ? 3 : HX_SCAN_CTAS)
+void linear_state_scan_kernel(const LinearStateArgs<T> a) {
+  constexpr int ROWS_PER_THREAD = 16;
+  constexpr int STRIDE = run_stride<ROWS_PER_THREAD>();
+  constexpr bool EXACT = sizeof(T) == 4;      // the float32 engine, see decayed_add_exact
+  extern __shared__ float4 shared4[];
+  float* shared = reinterpret_cast<float*>(shared4);
+  hx_pdl_prologue();
+  const int request = blockIdx.x;
+  const int head = blockIdx.y;
+  const int qk_head = head / (a.heads / a.qk_heads);
+  const int start = a.request_start[request];
+  const int count = ONE_TOKEN ? 1 : a.request_start[request + 1] - start;
+  const int parts = a.parts;
+  const int dim = a.dim;
+  const int vdim = a.vdim;
+  const int lane = blockIdx.z * a.block_lanes + threadIdx.x;
+  const int column = lane / parts;
+  const int part = lane - column * parts;
+  const bool live = column < vdim && threadIdx.x < a.block_lanes;
+  // staged per token: q, k (parts runs each), v [vdim], decay, beta
+  const int run = parts * STRIDE;
+  const int per_token = a.per_token;
+  const int lanes = vdim * parts;
+  float* s_state = a.state + static_cast<size_t>(a.request_slot[request]) * a.state_stride +
+                   static_cast<size_t>(head) * a.head_stride;
+  float S[ROWS_PER_THREAD];
+  float carry[EXACT ? ROWS_PER_THREAD : 1];
+#pragma unroll
+  for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+    const int n = part * ROWS_PER_THREAD + i;
+    S[i] = (live && n < dim) ? s_state[static_cast<size_t>(i) * lanes + lane] : 0.0f;
+    carry[EXACT ? i : 0] = 0.0f;
+  }
+  for (int i = threadIdx.x; i < (ONE_TOKEN ? 1 : a.tile) * per_token; i += blockDim.x)
+    shared[i] = 0.0f;
+  const float rate = a.decay_in != nullptr ? expf(a.a_log[head]) : 0.0f;
+  const float bias = a.decay_in != nullptr ? a.dt_bias[head] : 0.0f;
+  const float constant = a.decay_in != nullptr
+                             ? 0.0f
+                             : (EXACT ? a.fixed_decay_m1[head] : a.fixed_decay[head]);
+  const bool rotate = a.positions != nullptr && a.rotary_dim > 0;
+  const float load_q_scale = a.unit_norm ? 1.0f : a.q_scale;
+  const float load_k_scale = a.unit_norm ? 1.0f : a.k_scale;
+  for (int base = 0; base < count; base += a.tile) {
+    const int here = min(a.tile, count - base);
+    const size_t first = static_cast<size_t>(start + base);
+    __syncthreads();
+    const T* q = a.q + first * a.ld_q + qk_head * dim;
+    const T* k = a.k + first * a.ld_k + qk_head * dim;
+    const T* v = a.v + first * a.ld_v + head * vdim;
+    auto prepared = [&](const T* rows, int ld, float scale) {
+      return [=](int t, int e) -> float {
+        float x = hx_to_float<T>(rows[static_cast<size_t>(t) * ld + e]);
+        if (rotate && e < a.rotary_dim) {
+          int pair, partner;
+          bool leads;
+          if (a.rotary_layout == 0) {
+            pair = e >> 1; partner = e ^ 1; leads = (e & 1) == 0;
+          } else {
+            const int half = a.rotary_dim >> 1;
+            leads = e < half;
+            pair = leads ? e : e - half;
+            partner = leads ? e + half : e - half;
+          }
+          const float y = hx_to_float<T>(rows[static_cast<size_t>(t) * ld + partner]);
+          const int position = a.positions[first + t];
+          float sine, cosine;
+          if (EXACT) {
+            double s, c;
+            sincos(static_cast<double>(position) * a.freq_exact[pair], &s, &c);
+            sine = static_cast<float>(s); cosine = static_cast<float>(c);
+          } else {
+            sincosf(static_cast<float>(position) * a.freq[pair], &sine, &cosine);
+          }
+          x = leads ? x * cosine - y * sine : x * cosine + y * sine;
+        }
+        return x * scale;
+      };
+    };
+    stage<ONE_TOKEN>(shared, per_token, here, dim, prepared(q, a.ld_q, load_q_scale),
+                     padded<ROWS_PER_THREAD>);
+    stage<ONE_TOKEN>(shared + run, per_token, here, dim, prepared(k, a.ld_k, load_k_scale),
+                     padded<ROWS_PER_THREAD>);
+    stage<ONE_TOKEN>(shared + 2 * run, per_token, here, vdim,
+          [&](int t, int e) { return hx_to_float<T>(v[static_cast<size_t>(t) * a.ld_v + e]); },
+          [](int e) { return e; });
+    for (int t = threadIdx.x; t < here; t += blockDim.x) {
+      float decay = constant, beta = 1.0f;
+      if (a.decay_in != nullptr) {
+        const float step =
+            softplus(hx_to_float<T>(a.decay_in[(first + t) * a.ld_gates + head]) + bias);
+        decay = EXACT ? expm1f(-rate * step) : expf(-rate * step);
+      }
+      if (DELTA) beta = hx_sigmoid(hx_to_float<T>(a.beta_in[(first + t) * a.ld_gates + head]));
+      shared[t * per_token + 2 * run + vdim] = decay;
+      shared[t * per_token + 2 * run + vdim + 1] = beta;
+    }
+    if (a.unit_norm) {
+      // the padding between and behind the runs is zero, so the sums may run over all of it
+      __syncthreads();
+      const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5, in_warp = threadIdx.x & 31;
+      for (int t = warp; t < here; t += warps) {
+        float* qrow = shared + t * per_token;
+        float* krow = qrow + run;
+        float sq = 0.0f, sk = 0.0f;
+        for (int e = in_warp; e < run; e += 32) {
+          sq = fmaf(qrow[e], qrow[e], sq);
+          sk = fmaf(krow[e], krow[e], sk);
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+          sq += __shfl_xor_sync(0xffffffffu, sq, offset);
+          sk += __shfl_xor_sync(0xffffffffu, sk, offset);
+        }
+        const float fq = a.q_scale / sqrtf(sq + a.unit_eps);
+        const float fk = a.k_scale / sqrtf(sk + a.unit_eps);
+        for (int e = in_warp; e < run; e += 32) {
+          qrow[e] *= fq;
+          krow[e] *= fk;
+        }
+      }
+    }
+    __syncthreads();
+    float* o_out = a.o + first * (a.heads * vdim) + head * vdim + column;
+#pragma unroll 1
+    for (int t = 0; t < here; ++t) {
+      const float* row = shared + t * per_token;
+      const float4* q4 = reinterpret_cast<const float4*>(row + part * STRIDE);
+      const float4* k4 = reinterpret_cast<const float4*>(row + run + part * STRIDE);
+      const float vj = live ? row[2 * run + column] : 0.0f;
+      const float decay = row[2 * run + vdim];     // EXACT: the decay minus one
+      float u = vj;
+      if (DELTA) {
+        const float beta = row[2 * run + vdim + 1];
+        float dot0 = 0.0f, dot1 = 0.0f;
+#pragma unroll
+        for (int c = 0; c < ROWS_PER_THREAD / 4; ++c) {
+          const float4 kv = k4[c];
+          if constexpr (EXACT) {
+            dot0 = fmaf(S[4 * c + 0] + carry[4 * c + 0], kv.x, dot0);
+            dot1 = fmaf(S[4 * c + 1] + carry[4 * c + 1], kv.y, dot1);
+            dot0 = fmaf(S[4 * c + 2] + carry[4 * c + 2], kv.z, dot0);
+            dot1 = fmaf(S[4 * c + 3] + carry[4 * c + 3], kv.w, dot1);
+          } else {
+            dot0 = fmaf(S[4 * c + 0], kv.x, dot0);
+            dot1 = fmaf(S[4 * c + 1], kv.y, dot1);
+            dot0 = fmaf(S[4 * c + 2], kv.z, dot0);
+            dot1 = fmaf(S[4 * c + 3], kv.w, dot1);
+          }
+        }
+        float dot = dot0 + dot1;
+        for (int offset = parts >> 1; offset > 0; offset >>= 1)
+          dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+        // what the decayed matrix holds for this key
+        const float held = EXACT ? fmaf(decay, dot, dot) : decay * dot;
+        u = beta * (vj - held);
+      }
+      float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+      for (int c = 0; c < ROWS_PER_THREAD / 4; ++c) {
+        const float4 qv = q4[c];
+        const float4 kv = k4[c];
+        if constexpr (EXACT) {
+          decayed_add_exact(S[4 * c + 0], carry[4 * c + 0], decay, kv.x * u);
+          decayed_add_exact(S[4 * c + 1], carry[4 * c + 1], decay, kv.y * u);
+          decayed_add_exact(S[4 * c + 2], carry[4 * c + 2], decay, kv.z * u);
+          decayed_add_exact(S[4 * c + 3], carry[4 * c + 3], decay, kv.w * u);
+          sum0 = fmaf(S[4 * c + 0] + carry[4 * c + 0], qv.x, sum0);
+          sum1 = fmaf(S[4 * c + 1] + carry[4 * c + 1], qv.y, sum1);
+          sum0 = fmaf(S[4 * c + 2] + carry[4 * c + 2], qv.z, sum0);
+          sum1 = fmaf(S[4 * c + 3] + carry[4 * c + 3], qv.w, sum1);
+        } else {
+          S[4 * c + 0] = fmaf(decay, S[4 * c + 0], kv.x * u);
+          S[4 * c + 1] = fmaf(decay, S[4 * c + 1], kv.y * u);
+          S[4 * c + 2] = fmaf(decay, S[4 * c + 2], kv.z * u);
+          S[4 * c + 3] = fmaf(decay, S[4 * c + 3], kv.w * u);
+          sum0 = fmaf(S[4 * c + 0], qv.x, sum0);
+          sum1 = fmaf(S[4 * c + 1], qv.y, sum1);
+          sum0 = fmaf(S[4 * c + 2], qv.z, sum0);
+          sum1 = fmaf(S[4 * c + 3], qv.w, sum1);
+        }
+      }
+      float sum = sum0 + sum1;
+      for (int offset = parts >> 1; offset > 0; offset >>= 1)
+        sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+      if (live && part == 0) o_out[static_cast<size_t>(t) * (a.heads * vdim)] = sum;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < ROWS_PER_THREAD; ++i) {
+      const int n = part * ROWS_PER_THREAD + i;
+      if (n < dim)
+        s_state[static_cast<size_t>(i) * lanes + lane] = EXACT ? S[i] + carry[EXACT ? i : 0] : S[i];
+    }
+  }
+}
+
 // ----------------------------------------------------------------- gated group norm
 
 // Channels in `groups` equal parts, each divided by its own root mean square (eps inside the
@@ -744,6 +985,92 @@ HX_API int hx_outer_product_scan(const void* r, int ld_r, const void* k, int ld_
     HX_REQUIRE(false, "hx_outer_product_scan: unknown dtype %d", dtype);
   }
   HX_CHECK_LAUNCH("hx_outer_product_scan");
+  return HX_OK;
+}
+
+namespace {
+template <typename T>
+void launch_linear_state(const LinearStateArgs<T>& a, bool delta, bool one_token, dim3 grid,
+                         int threads, size_t shared_bytes, size_t one_bytes, cudaStream_t stream) {
+  if (delta) {
+    if (one_token) hx_launch(linear_state_scan_kernel<T, true, true>, grid, threads, one_bytes, stream, a);
+    else hx_launch(linear_state_scan_kernel<T, true, false>, grid, threads, shared_bytes, stream, a);
+  } else {
+    if (one_token) hx_launch(linear_state_scan_kernel<T, false, true>, grid, threads, one_bytes, stream, a);
+    else hx_launch(linear_state_scan_kernel<T, false, false>, grid, threads, shared_bytes, stream, a);
+  }
+}
+}  // namespace
+
+// Linear attention with a [dim x vdim] matrix per head (see LinearStateArgs).  q, k
+// [tokens, qk_heads * dim] and v [tokens, heads * vdim] in the compute dtype; `decay_in` and
+// `beta_in` are columns of projected rows (one per head) or null (then `fixed_decay` and
+// `fixed_decay_m1` [heads] give the head's constant decay and the same minus one);
+// delta != 0 needs `beta_in`.  Rotation: `positions` with `freq` (and `freq_exact` in the
+// float32 engine), or null.  o [tokens, heads * vdim] float32.
+HX_API int hx_linear_state_scan(const void* q, int ld_q, const void* k, int ld_k, const void* v,
+                                int ld_v, int dtype, int delta, const void* decay_in,
+                                const void* beta_in, int ld_gates, const float* a_log,
+                                const float* dt_bias, const float* fixed_decay,
+                                const float* fixed_decay_m1, const int* positions,
+                                const float* freq, const double* freq_exact, int rotary_dim,
+                                int rotary_layout, int unit_norm, float unit_eps, float q_scale,
+                                float k_scale, float* state, long long state_stride,
+                                int head_stride, float* o, const int* request_start,
+                                const int* request_slot, int requests, int tokens, int heads,
+                                int qk_heads, int dim, int vdim, cudaStream_t stream) {
+  HX_REQUIRE(requests >= 0 && heads > 0 && qk_heads > 0 && dim > 0 && vdim > 0,
+             "hx_linear_state_scan: bad sizes");
+  HX_REQUIRE(heads % qk_heads == 0,
+             "hx_linear_state_scan: heads must be a multiple of the query/key heads");
+  HX_REQUIRE(!delta || beta_in != nullptr, "hx_linear_state_scan: the delta rule needs beta");
+  HX_REQUIRE(decay_in != nullptr ? (a_log != nullptr && dt_bias != nullptr)
+                                 : (fixed_decay != nullptr && fixed_decay_m1 != nullptr),
+             "hx_linear_state_scan: a decay needs its rate and bias, or the heads' constants");
+  HX_REQUIRE(positions == nullptr || rotary_dim == 0 ||
+                 (rotary_dim % 2 == 0 && rotary_dim <= dim && freq != nullptr &&
+                  (dtype != HX_F32 || freq_exact != nullptr)),
+             "hx_linear_state_scan: rotation over %d of %d coordinates", rotary_dim, dim);
+  const int parts = parts_for(dim);
+  HX_REQUIRE(parts > 0, "hx_linear_state_scan: heads of %d are more than %d", dim, 32 * 16);
+  const int block_lanes = min(vdim, SCAN_THREADS / parts) * parts;
+  const int threads = (block_lanes + 31) / 32 * 32;
+  const int column_blocks = (vdim * parts + block_lanes - 1) / block_lanes;
+  HX_REQUIRE(head_stride >= state_floats(vdim, dim),
+             "hx_linear_state_scan: a head's state takes %d floats, not %d", state_floats(vdim, dim),
+             head_stride);
+  const int per_token = staged_floats(2, dim, vdim + 2);
+  const int tile = tile_for(per_token);
+  HX_REQUIRE(tile >= 1, "hx_linear_state_scan: a token's vectors do not fit shared memory");
+  if (requests == 0) return HX_OK;
+  const dim3 grid(requests, heads, column_blocks);
+  const size_t shared_bytes = static_cast<size_t>(tile) * per_token * sizeof(float);
+  const bool one_token = tokens == requests;
+  const size_t one_bytes = static_cast<size_t>(per_token) * sizeof(float);
+  if (dtype == HX_F32) {
+    LinearStateArgs<float> a{static_cast<const float*>(q), static_cast<const float*>(k),
+                             static_cast<const float*>(v), ld_q, ld_k, ld_v,
+                             static_cast<const float*>(decay_in), static_cast<const float*>(beta_in),
+                             ld_gates, a_log, dt_bias, fixed_decay, fixed_decay_m1, positions, freq,
+                             freq_exact, rotary_dim, rotary_layout, unit_norm, unit_eps, q_scale,
+                             k_scale, state, state_stride, head_stride, o, request_start,
+                             request_slot, heads, qk_heads, dim, vdim, parts, block_lanes, tile,
+                             per_token};
+    launch_linear_state(a, delta != 0, one_token, grid, threads, shared_bytes, one_bytes, stream);
+  } else if (dtype == HX_BF16) {
+    LinearStateArgs<__nv_bfloat16> a{
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+        static_cast<const __nv_bfloat16*>(v), ld_q, ld_k, ld_v,
+        static_cast<const __nv_bfloat16*>(decay_in), static_cast<const __nv_bfloat16*>(beta_in),
+        ld_gates, a_log, dt_bias, fixed_decay, fixed_decay_m1, positions, freq, freq_exact,
+        rotary_dim, rotary_layout, unit_norm, unit_eps, q_scale, k_scale, state, state_stride,
+        head_stride, o, request_start, request_slot, heads, qk_heads, dim, vdim, parts,
+        block_lanes, tile, per_token};
+    launch_linear_state(a, delta != 0, one_token, grid, threads, shared_bytes, one_bytes, stream);
+  } else {
+    HX_REQUIRE(false, "hx_linear_state_scan: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_linear_state_scan");
   return HX_OK;
 }
 

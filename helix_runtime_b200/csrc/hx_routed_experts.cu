@@ -1,0 +1,255 @@
+// A feed-forward of routed experts: every token goes through `top` of `experts` small gated
+// feed-forwards, chosen by a router, and their outputs are summed with the router's weights.
+//
+//   * hx_route_top: scores s = sigmoid(z) of the router's float32 sums z, the `top` largest
+//     (the lowest index among equals), weights s / (sum of the chosen + 1e-20) * scale;
+//   * hx_expert_gate_up: act[pair] = f(Wg[e] x) * (Wu[e] x) for every (token, choice) pair;
+//   * hx_expert_down: out[token] += sum_k weight_k * Wd[e_k] act[pair_k], the choices in
+//     ascending order, one writer per output (no atomics: the sum's order is fixed).
+//
+// The two products read the expert's matrices through the chosen index, a row per warp: with
+// few tokens (decoding) that is the stream of the chosen experts' weights, which is all such a
+// step has to move.  Nothing here looks at device values on the host, so a step can be
+// recorded into a CUDA graph.
+#include "hx_common.cuh"
+
+namespace {
+
+constexpr int ROUTE_MAX_PER_LANE = 32;      // experts a lane can mark as taken: 1,024 in all
+
+__global__ __launch_bounds__(128) void route_top_kernel(const float* __restrict__ sums, int ld,
+                                                        int tokens, int experts, int top,
+                                                        float scale, int* __restrict__ chosen,
+                                                        float* __restrict__ weights) {
+  hx_pdl_prologue();
+  const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (token >= tokens) return;
+  const int lane = threadIdx.x & 31;
+  const float* z = sums + static_cast<size_t>(token) * ld;
+  unsigned taken = 0u;          // bit i: expert lane + 32 i is chosen already
+  float total = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.0f;         // scores lie in [0, 1]
+    int best_index = 0x7fffffff;
+    for (int i = 0, e = lane; e < experts; ++i, e += 32) {
+      if (taken & (1u << i)) continue;
+      const float s = hx_sigmoid(z[e]);
+      if (s > best) { best = s; best_index = e; }      // ascending e: the first of equals stays
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
+      if (other > best || (other == best && other_index < best_index)) {
+        best = other;
+        best_index = other_index;
+      }
+    }
+    if ((best_index & 31) == lane && best_index < experts) taken |= 1u << (best_index >> 5);
+    total += best;
+    if (lane == 0) {
+      chosen[static_cast<size_t>(token) * top + k] = best_index;
+      weights[static_cast<size_t>(token) * top + k] = best;
+    }
+  }
+  __syncwarp();
+  if (lane < top) {
+    float* w = weights + static_cast<size_t>(token) * top + lane;
+    *w = *w / (total + 1e-20f) * scale;
+  }
+}
+
+// sum over a lane's share of w[0..width) * x[0..width), x float32 in shared memory
+template <typename T>
+__device__ __forceinline__ float lane_dot(const T* __restrict__ w, const float* x, int width,
+                                          int lane);
+
+template <>
+__device__ __forceinline__ float lane_dot<float>(const float* __restrict__ w, const float* x,
+                                                 int width, int lane) {
+  float sum = 0.0f;
+  if ((width & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    for (int c = lane * 4; c < width; c += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(w + c);
+      const float4 b = *reinterpret_cast<const float4*>(x + c);
+      sum = fmaf(a.x, b.x, sum); sum = fmaf(a.y, b.y, sum);
+      sum = fmaf(a.z, b.z, sum); sum = fmaf(a.w, b.w, sum);
+    }
+  } else {
+    for (int c = lane; c < width; c += 32) sum = fmaf(w[c], x[c], sum);
+  }
+  return sum;
+}
+
+template <>
+__device__ __forceinline__ float lane_dot<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w,
+                                                         const float* x, int width, int lane) {
+  float sum = 0.0f;
+  if ((width & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    for (int c = lane * 8; c < width; c += 256) {
+      const uint4 packed = *reinterpret_cast<const uint4*>(w + c);
+      const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&packed);
+      const float4 x0 = *reinterpret_cast<const float4*>(x + c);
+      const float4 x1 = *reinterpret_cast<const float4*>(x + c + 4);
+      const float2 a = __bfloat1622float2(pairs[0]), b = __bfloat1622float2(pairs[1]);
+      const float2 d = __bfloat1622float2(pairs[2]), e = __bfloat1622float2(pairs[3]);
+      sum = fmaf(a.x, x0.x, sum); sum = fmaf(a.y, x0.y, sum);
+      sum = fmaf(b.x, x0.z, sum); sum = fmaf(b.y, x0.w, sum);
+      sum = fmaf(d.x, x1.x, sum); sum = fmaf(d.y, x1.y, sum);
+      sum = fmaf(e.x, x1.z, sum); sum = fmaf(e.y, x1.w, sum);
+    }
+  } else {
+    for (int c = lane; c < width; c += 32) sum = fmaf(__bfloat162float(w[c]), x[c], sum);
+  }
+  return sum;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  return v;
+}
+
+constexpr int EXPERT_WARPS = 4;
+constexpr int GATE_UP_ROWS = 32;      // activation rows a CTA of the first product computes
+constexpr int DOWN_ROWS = 32;         // output rows a CTA of the second product computes
+
+// grid (pairs, ceil(ff / GATE_UP_ROWS)); shared: the token's input row in float32
+template <typename T>
+__global__ __launch_bounds__(EXPERT_WARPS * 32) void expert_gate_up_kernel(
+    const T* __restrict__ x, int ld_x, const T* __restrict__ gate_up, const int* __restrict__ chosen,
+    T* __restrict__ act, int top, int ff, int width, int experts, int activation) {
+  extern __shared__ float4 shared4[];
+  float* xs = reinterpret_cast<float*>(shared4);
+  hx_pdl_prologue();
+  const int pair = blockIdx.x;
+  const int token = pair / top;
+  const int expert = chosen[pair];
+  if (expert < 0 || expert >= experts) return;
+  const T* xr = x + static_cast<size_t>(token) * ld_x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = hx_to_float<T>(xr[c]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* w = gate_up + static_cast<size_t>(expert) * 2 * ff * width;
+  const int first = blockIdx.y * GATE_UP_ROWS;
+  for (int j = first + warp; j < first + GATE_UP_ROWS && j < ff; j += EXPERT_WARPS) {
+    const float g = warp_sum(lane_dot<T>(w + static_cast<size_t>(j) * width, xs, width, lane));
+    const float u = warp_sum(lane_dot<T>(w + static_cast<size_t>(ff + j) * width, xs, width, lane));
+    if (lane == 0)
+      act[static_cast<size_t>(pair) * ff + j] = hx_from_float<T>(hx_gate(g, activation) * u);
+  }
+}
+
+// grid (tokens, ceil(width / DOWN_ROWS)); shared: one activation row in float32 at a time
+template <typename T>
+__global__ __launch_bounds__(EXPERT_WARPS * 32) void expert_down_kernel(
+    const T* __restrict__ act, const T* __restrict__ down, const int* __restrict__ chosen,
+    const float* __restrict__ weights, float* __restrict__ out, int ld_out, int top, int ff,
+    int width, int experts) {
+  extern __shared__ float4 shared4[];
+  float* as = reinterpret_cast<float*>(shared4);
+  hx_pdl_prologue();
+  const int token = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int first = blockIdx.y * DOWN_ROWS;
+  constexpr int PER_WARP = DOWN_ROWS / EXPERT_WARPS;
+  float sums[PER_WARP];
+#pragma unroll
+  for (int r = 0; r < PER_WARP; ++r) sums[r] = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    const int pair = token * top + k;
+    const int expert = chosen[pair];
+    const float weight = weights[pair];
+    __syncthreads();
+    for (int c = threadIdx.x; c < ff; c += blockDim.x)
+      as[c] = hx_to_float<T>(act[static_cast<size_t>(pair) * ff + c]);
+    __syncthreads();
+    if (expert < 0 || expert >= experts) continue;
+    const T* w = down + static_cast<size_t>(expert) * width * ff;
+#pragma unroll
+    for (int r = 0; r < PER_WARP; ++r) {
+      const int i = first + warp + r * EXPERT_WARPS;
+      if (i < width)
+        sums[r] = fmaf(weight, warp_sum(lane_dot<T>(w + static_cast<size_t>(i) * ff, as, ff, lane)),
+                       sums[r]);
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < PER_WARP; ++r) {
+      const int i = first + warp + r * EXPERT_WARPS;
+      if (i < width) out[static_cast<size_t>(token) * ld_out + i] += sums[r];
+    }
+  }
+}
+
+}  // namespace
+
+// sums float32 [tokens, ld] (the router's products); chosen int32 and weights float32
+// [tokens, top].
+HX_API int hx_route_top(const float* sums, int ld, int tokens, int experts, int top, float scale,
+                        int* chosen, float* weights, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts && ld >= experts,
+             "hx_route_top: bad sizes");
+  HX_REQUIRE(experts <= 32 * ROUTE_MAX_PER_LANE && top <= 32,
+             "hx_route_top: at most %d experts and 32 choices", 32 * ROUTE_MAX_PER_LANE);
+  if (tokens == 0) return HX_OK;
+  hx_launch(route_top_kernel, dim3((tokens + 3) / 4), 128, 0, stream, sums, ld, tokens, experts,
+            top, scale, chosen, weights);
+  HX_CHECK_LAUNCH("hx_route_top");
+  return HX_OK;
+}
+
+// x [tokens, ld_x], gate_up [experts, 2 * ff, width] (gate rows, then up rows), act
+// [tokens * top, ff], all in the compute dtype; chosen int32 [tokens, top].
+HX_API int hx_expert_gate_up(const void* x, int ld_x, const void* gate_up, const int* chosen,
+                             void* act, int dtype, int tokens, int top, int ff, int width,
+                             int experts, int activation, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && top > 0 && ff > 0 && width > 0 && experts > 0 && ld_x >= width,
+             "hx_expert_gate_up: bad sizes");
+  HX_REQUIRE(width * sizeof(float) <= 48 * 1024, "hx_expert_gate_up: rows of %d are too wide",
+             width);
+  if (tokens == 0) return HX_OK;
+  const dim3 grid(tokens * top, (ff + GATE_UP_ROWS - 1) / GATE_UP_ROWS);
+  const size_t shared = (static_cast<size_t>(width) * sizeof(float) + 15) / 16 * 16;
+  if (dtype == HX_F32) {
+    hx_launch(expert_gate_up_kernel<float>, grid, EXPERT_WARPS * 32, shared, stream,
+              static_cast<const float*>(x), ld_x, static_cast<const float*>(gate_up), chosen,
+              static_cast<float*>(act), top, ff, width, experts, activation);
+  } else if (dtype == HX_BF16) {
+    hx_launch(expert_gate_up_kernel<__nv_bfloat16>, grid, EXPERT_WARPS * 32, shared, stream,
+              static_cast<const __nv_bfloat16*>(x), ld_x,
+              static_cast<const __nv_bfloat16*>(gate_up), chosen, static_cast<__nv_bfloat16*>(act),
+              top, ff, width, experts, activation);
+  } else {
+    HX_REQUIRE(false, "hx_expert_gate_up: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_expert_gate_up");
+  return HX_OK;
+}
+
+// act [tokens * top, ff] and down [experts, width, ff] in the compute dtype; out float32
+// [tokens, ld_out] is summed into.
+HX_API int hx_expert_down(const void* act, const void* down, const int* chosen,
+                          const float* weights, float* out, int ld_out, int dtype, int tokens,
+                          int top, int ff, int width, int experts, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && top > 0 && ff > 0 && width > 0 && experts > 0 && ld_out >= width,
+             "hx_expert_down: bad sizes");
+  HX_REQUIRE(ff * sizeof(float) <= 48 * 1024, "hx_expert_down: experts of %d are too wide", ff);
+  if (tokens == 0) return HX_OK;
+  const dim3 grid(tokens, (width + DOWN_ROWS - 1) / DOWN_ROWS);
+  const size_t shared = (static_cast<size_t>(ff) * sizeof(float) + 15) / 16 * 16;
+  if (dtype == HX_F32) {
+    hx_launch(expert_down_kernel<float>, grid, EXPERT_WARPS * 32, shared, stream,
+              static_cast<const float*>(act), static_cast<const float*>(down), chosen, weights,
+              out, ld_out, top, ff, width, experts);
+  } else if (dtype == HX_BF16) {
+    hx_launch(expert_down_kernel<__nv_bfloat16>, grid, EXPERT_WARPS * 32, shared, stream,
+              static_cast<const __nv_bfloat16*>(act), static_cast<const __nv_bfloat16*>(down),
+              chosen, weights, out, ld_out, top, ff, width, experts);
+  } else {
+    HX_REQUIRE(false, "hx_expert_down: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_expert_down");
+  return HX_OK;
+}

@@ -136,6 +136,10 @@ class DecoderModel:
         self.embedding = build_part("embedding", spec.embedding, spec.hidden_size)
         self.blocks: List[Block] = [Block(block, spec.hidden_size) for block in spec.blocks]
         self.schedule = spec.schedule
+        # parts that run before a schedule entry, by the entry's index
+        self.entry_parts = {index: build_part("entry", entry.before, spec.hidden_size)
+                            for index, entry in enumerate(spec.schedule)
+                            if entry.before is not None}
         self.final_norm: Norm = build_part("norm", spec.final_norm, spec.hidden_size)
         self.lm_head = build_part("lm_head", spec.lm_head, spec.hidden_size)
         self.dtype: Optional[torch.dtype] = None
@@ -149,6 +153,7 @@ class DecoderModel:
         yield self.embedding
         for block in self.blocks:
             yield from block.parts()
+        yield from self.entry_parts.values()
         yield self.final_norm
         yield self.lm_head
 
@@ -180,6 +185,7 @@ class DecoderModel:
         total = self.final_norm.weight_bytes() + self.lm_head.weight_bytes()
         for entry in self.schedule:
             total += sum(part.weight_bytes() for part in self.blocks[entry.block].parts())
+        total += sum(part.weight_bytes() for part in self.entry_parts.values())
         return total
 
     # -------------------------------------------------------------------- cache
@@ -242,7 +248,7 @@ class DecoderModel:
             ops.streams_spread(first, residual, ctx.n_tokens, self.streams)
         else:
             self.embedding.forward(ctx, residual)
-        if any(entry.add_embedding for entry in self.schedule):
+        if any(entry.add_embedding for entry in self.schedule) or self.entry_parts:
             if self.streams > 1:
                 raise ValueError("adding the embedding back in is defined for one residual stream")
             # the embedding's output is kept for the entries that add it back in
@@ -251,6 +257,8 @@ class DecoderModel:
         for index, entry in enumerate(self.schedule):
             if entry.add_embedding:
                 ops.add_rows(residual, embedded, ctx.n_tokens)
+            if index in self.entry_parts:
+                self.entry_parts[index].forward(ctx, residual, embedded)
             self.blocks[entry.block].forward(ctx, self.layer_cache(cache, index), residual, normed)
             if self.after_entry is not None:
                 rows = residual[:ctx.n_tokens]

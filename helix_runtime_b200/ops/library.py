@@ -160,6 +160,33 @@ def _declare(library: ctypes.CDLL) -> None:
         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
     library.hx_rotate_back.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                        _c_int, _c_int, _c_ptr]
+    _c_double_ptr = _c_ptr
+    library.hx_linear_state_scan.argtypes = [
+        _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
+        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_double_ptr, _c_int, _c_int, _c_int,
+        _c_float, _c_float, _c_float, _c_ptr, _c_longlong, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_gated_residual_add.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
+                                              _c_ptr]
+    library.hx_join_rows.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_route_top.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr,
+                                     _c_ptr]
+    library.hx_expert_gate_up.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_expert_down.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                       _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_latent_prepare.argtypes = [
+        _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr,
+        _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_latent_queries.argtypes = [
+        _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_head_products.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
+                                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    for name in ("hx_linear_state_scan", "hx_gated_residual_add", "hx_join_rows", "hx_route_top",
+                 "hx_expert_gate_up", "hx_expert_down", "hx_latent_prepare", "hx_latent_queries",
+                 "hx_head_products"):
+        getattr(library, name).restype = _c_int
     for name in ("hx_streams_spread", "hx_streams_read_norm", "hx_streams_write", "hx_scaled_sum",
                  "hx_add_bias", "hx_biased_activation", "hx_causal_filter", "hx_state_space_scan",
                  "hx_token_shift", "hx_outer_product_scan", "hx_gated_group_norm",
@@ -811,6 +838,178 @@ def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, 
                                      dtype_code(out.dtype), weight.data_ptr(), out.data_ptr(),
                                      out.stride(0), tokens, channels, groups, float(eps),
                                      1 if gate_after else 0, _stream()))
+
+
+# ----------------------------------------------- linear attention with a matrix state
+
+def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor,
+                      o: torch.Tensor, request_start: torch.Tensor, request_slot: torch.Tensor,
+                      requests: int, heads: int, qk_heads: int, dim: int, vdim: int, *,
+                      delta: bool, decay_in: Optional[torch.Tensor] = None,
+                      beta_in: Optional[torch.Tensor] = None,
+                      a_log: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None,
+                      fixed_decay: Optional[torch.Tensor] = None,
+                      fixed_decay_m1: Optional[torch.Tensor] = None,
+                      positions: Optional[torch.Tensor] = None,
+                      freq: Optional[torch.Tensor] = None,
+                      freq_exact: Optional[torch.Tensor] = None, rotary_dim: int = 0,
+                      rotary_layout: int = 1, unit_norm: bool = False, unit_eps: float = 0.0,
+                      q_scale: float = 1.0, k_scale: float = 1.0,
+                      tokens: Optional[int] = None) -> None:
+    """Linear attention with one ``[dim, vdim]`` matrix per head, token by token along each
+    request: ``S <- g S + k v'`` (plain) or ``S <- g S; u = beta (v - S' k); S <- S + k u'``
+    (``delta``), then ``o = S' q``.  ``q, k`` ``[tokens, qk_heads * dim]`` and ``v``
+    ``[tokens, heads * vdim]`` in the compute dtype (views with a row stride).  The decay is
+    ``exp(-exp(a_log) softplus(decay_in + dt_bias))`` from the column ``decay_in[:, head]``, or
+    the head's constant ``fixed_decay`` (with ``fixed_decay_m1``, the same minus one); ``beta =
+    sigmoid(beta_in[:, head])``.  Queries and keys are prepared in float32: unit vectors per
+    head (``unit_norm``: ``x / sqrt(sum x^2 + unit_eps)``) or rotated over their first
+    ``rotary_dim`` coordinates by ``positions * freq`` (layout as ``ROTARY_LAYOUTS``), then
+    times ``q_scale`` / ``k_scale``.  ``state`` ``[slots, >= heads * scan_state_floats(vdim,
+    dim)]`` and ``o`` ``[tokens, heads * vdim]`` float32."""
+    _need(state, torch.float32, "state")
+    _need(o, torch.float32, "o")
+    assert q.dtype == k.dtype == v.dtype and q.stride(-1) == k.stride(-1) == v.stride(-1) == 1
+    assert o.is_contiguous() and o.shape[1] == heads * vdim
+    head_stride = scan_state_floats(vdim, dim)
+    assert state.shape[1] >= heads * head_stride
+    ld_gates = 0
+    for gate in (decay_in, beta_in):
+        if gate is not None:
+            assert gate.dtype == q.dtype and gate.stride(-1) == 1
+            assert ld_gates in (0, gate.stride(0))
+            ld_gates = gate.stride(0)
+    for name, tensor in (("a_log", a_log), ("dt_bias", dt_bias), ("fixed_decay", fixed_decay),
+                         ("fixed_decay_m1", fixed_decay_m1), ("freq", freq)):
+        if tensor is not None:
+            _need(tensor, torch.float32, name)
+    if freq_exact is not None:
+        _need(freq_exact, torch.float64, "freq_exact")
+    _check(lib().hx_linear_state_scan(
+        q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+        dtype_code(q.dtype), 1 if delta else 0, _ptr(decay_in), _ptr(beta_in), ld_gates,
+        _ptr(a_log), _ptr(dt_bias), _ptr(fixed_decay), _ptr(fixed_decay_m1), _ptr(positions),
+        _ptr(freq), _ptr(freq_exact), rotary_dim, rotary_layout, 1 if unit_norm else 0,
+        float(unit_eps), float(q_scale), float(k_scale), state.data_ptr(), state.stride(0),
+        head_stride, o.data_ptr(), request_start.data_ptr(), request_slot.data_ptr(), requests,
+        q.shape[0] if tokens is None else tokens, heads, qk_heads, dim, vdim, _stream()))
+
+
+# ------------------------------------------------------------- gated residual connection
+
+def gated_residual_add(residual: torch.Tensor, output: torch.Tensor, gate: torch.Tensor,
+                       bias: torch.Tensor, tokens: int) -> None:
+    """residual[:tokens] += output[:tokens] * sigmoid(gate[:tokens] + bias); all float32."""
+    for name, tensor in (("residual", residual), ("output", output), ("gate", gate),
+                         ("bias", bias)):
+        _need(tensor, torch.float32, name)
+    width = residual.shape[1]
+    assert residual.is_contiguous() and output.is_contiguous() and output.shape[1] == width
+    assert gate.shape[1] >= width and bias.numel() == width
+    _check(lib().hx_gated_residual_add(residual.data_ptr(), output.data_ptr(), gate.data_ptr(),
+                                       gate.stride(0), bias.data_ptr(), tokens, width, _stream()))
+
+
+def join_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, tokens: int) -> None:
+    """out[:tokens] = [a[:tokens] | b[:tokens]] in ``out``'s dtype; ``a``, ``b`` float32."""
+    _need(a, torch.float32, "a")
+    _need(b, torch.float32, "b")
+    width = a.shape[1]
+    assert a.is_contiguous() and b.is_contiguous() and b.shape[1] == width
+    assert out.stride(-1) == 1 and out.shape[1] >= 2 * width
+    _check(lib().hx_join_rows(a.data_ptr(), b.data_ptr(), out.data_ptr(), out.stride(0),
+                              dtype_code(out.dtype), tokens, width, _stream()))
+
+
+# ------------------------------------------------------------------------ routed experts
+
+def route_top(sums: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, tokens: int,
+              experts: int, top: int, scale: float) -> None:
+    """Per token the ``top`` largest of ``sigmoid(sums[:, :experts])`` (lowest index among
+    equals) into ``chosen`` (int32 ``[tokens, top]``), and their scores over their sum
+    (``+ 1e-20``) times ``scale`` into ``weights`` (float32)."""
+    _need(sums, torch.float32, "sums")
+    _need(chosen, torch.int32, "chosen")
+    _need(weights, torch.float32, "weights")
+    assert chosen.is_contiguous() and weights.is_contiguous()
+    assert chosen.shape[1] == top and weights.shape[1] == top
+    _check(lib().hx_route_top(sums.data_ptr(), sums.stride(0), tokens, experts, top, float(scale),
+                              chosen.data_ptr(), weights.data_ptr(), _stream()))
+
+
+def expert_gate_up(x: torch.Tensor, gate_up: torch.Tensor, chosen: torch.Tensor,
+                   act: torch.Tensor, tokens: int, top: int, activation: int = GATE_SILU) -> None:
+    """act[t * top + k] = f(gate_e x[t]) * (up_e x[t]) with ``e = chosen[t, k]``; ``gate_up``
+    ``[experts, 2 * ff, width]`` holds an expert's gate rows, then its up rows."""
+    experts, rows, width = gate_up.shape
+    ff = rows // 2
+    assert x.dtype == gate_up.dtype == act.dtype and gate_up.is_contiguous()
+    assert x.stride(-1) == 1 and x.shape[1] == width
+    assert act.is_contiguous() and act.shape[1] == ff and act.shape[0] >= tokens * top
+    _check(lib().hx_expert_gate_up(x.data_ptr(), x.stride(0), gate_up.data_ptr(), chosen.data_ptr(),
+                                   act.data_ptr(), dtype_code(x.dtype), tokens, top, ff, width,
+                                   experts, int(activation), _stream()))
+
+
+def expert_down(act: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor,
+                weights: torch.Tensor, out: torch.Tensor, tokens: int, top: int) -> None:
+    """out[t] += sum_k weights[t, k] * down_e act[t * top + k] (``k`` ascending); ``down``
+    ``[experts, width, ff]``, ``out`` float32."""
+    experts, width, ff = down.shape
+    _need(out, torch.float32, "out")
+    assert act.dtype == down.dtype and down.is_contiguous() and act.is_contiguous()
+    assert act.shape[1] == ff and out.shape[1] >= width
+    _check(lib().hx_expert_down(act.data_ptr(), down.data_ptr(), chosen.data_ptr(),
+                                weights.data_ptr(), out.data_ptr(), out.stride(0),
+                                dtype_code(act.dtype), tokens, top, ff, width, experts, _stream()))
+
+
+# ---------------------------------------------------------- attention over a cached latent
+
+def latent_prepare(down: torch.Tensor, q_weight: torch.Tensor, kv_weight: torch.Tensor, eps: float,
+                   positions: torch.Tensor, freq: Optional[torch.Tensor],
+                   freq_exact: Optional[torch.Tensor], rotary_dims: int, layout: int,
+                   query_latent: torch.Tensor, rows: torch.Tensor, key_offset: int, tokens: int,
+                   q_rank: int, kv_rank: int, rot: int, row_dim: int) -> None:
+    """From the float32 down-projection ``[q_rank | kv_rank | rot]`` of every token: the normed
+    query latent into ``query_latent``; the key row ``[c | rot(kr) | 0]`` at column
+    ``key_offset`` of ``rows`` and the value row ``[c | 0]`` behind it (``row_dim`` wide each),
+    ``c`` the normed key/value latent."""
+    _need(down, torch.float32, "down")
+    _need(q_weight, torch.float32, "q_weight")
+    _need(kv_weight, torch.float32, "kv_weight")
+    assert query_latent.dtype == rows.dtype and down.stride(-1) == 1
+    _check(lib().hx_latent_prepare(
+        down.data_ptr(), down.stride(0), q_weight.data_ptr(), kv_weight.data_ptr(), float(eps),
+        positions.data_ptr(), _ptr(freq), _ptr(freq_exact), rotary_dims, layout,
+        query_latent.data_ptr(), query_latent.stride(0), rows.data_ptr(), rows.stride(0),
+        key_offset, dtype_code(rows.dtype), tokens, q_rank, kv_rank, rot, row_dim, _stream()))
+
+
+def latent_queries(q: torch.Tensor, rot_offset: int, rows: torch.Tensor, positions: torch.Tensor,
+                   freq: Optional[torch.Tensor], freq_exact: Optional[torch.Tensor],
+                   rotary_dims: int, layout: int, tokens: int, heads: int, kv_rank: int, rot: int,
+                   row_dim: int) -> None:
+    """The rotated part of every head's query (``q[:, rot_offset + head * rot:][:rot]``) turned
+    by the token's position into ``rows[:, head * row_dim + kv_rank:]``, zeros to the head's
+    end."""
+    assert q.dtype == rows.dtype and q.stride(-1) == 1 and rows.stride(-1) == 1
+    _check(lib().hx_latent_queries(q.data_ptr(), q.stride(0), rot_offset, rows.data_ptr(),
+                                   rows.stride(0), positions.data_ptr(), _ptr(freq),
+                                   _ptr(freq_exact), rotary_dims, layout, dtype_code(rows.dtype),
+                                   tokens, heads, kv_rank, rot, row_dim, _stream()))
+
+
+def head_products(x: torch.Tensor, x_stride: int, w: torch.Tensor, out: torch.Tensor,
+                  out_stride: int, tokens: int) -> None:
+    """out[t, h * out_stride + o] = sum_i w[h, o, i] * x[t, h * x_stride + i]: one small product
+    per head, ``w`` ``[heads, out_dim, in_dim]``, everything in the compute dtype."""
+    heads, out_dim, in_dim = w.shape
+    assert x.dtype == w.dtype == out.dtype and w.is_contiguous()
+    assert x.stride(-1) == 1 and out.stride(-1) == 1
+    _check(lib().hx_head_products(x.data_ptr(), x.stride(0), x_stride, w.data_ptr(),
+                                  out.data_ptr(), out.stride(0), out_stride, dtype_code(x.dtype),
+                                  tokens, heads, out_dim, in_dim, _stream()))
 
 
 # ------------------------------------------------- rotation from positions, normed heads

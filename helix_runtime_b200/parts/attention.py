@@ -264,31 +264,12 @@ class PagedAttention(Mixer):
         keys = max(32, -(-keys // 32) * 32)
         return min(keys, max(32, limit))
 
-    def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
-                residual: torch.Tensor) -> None:
+    def attend(self, ctx: StepContext, cache: LayerCache, qkv: torch.Tensor,
+               context: torch.Tensor) -> None:
+        """Scores, mask, softmax and weighted sum for the step's rows: queries from ``qkv``
+        (``heads`` rows of ``row_dim``), keys and values from the entry's pages, the result into
+        ``context``.  Chooses the kernels by the step's make-up."""
         n = ctx.n_tokens
-        # scratch is named by its width: layers of different sizes each keep their own buffer
-        # (a name whose shape changed from layer to layer would be replaced at every call)
-        qkv = ctx.workspace.get(f"attention.qkv/{self.projected_size}",
-                                (ctx.capacity, self.projected_size), ctx.dtype)
-        context = ctx.workspace.get(f"attention.context/{self.q_size}",
-                                    (ctx.capacity, self.q_size), ctx.dtype)
-        uncleared = gate_rows = None
-        if self.conv_taps > 1:
-            uncleared, gate_rows = self.project_filtered(ctx, cache, x, qkv)
-        elif is_weight_stream(x, self.w_qkv, n):
-            # few tokens: split-K into a float32 accumulator that the rotary kernel reads,
-            # rounds as the product's store would have, and clears
-            accumulator = ctx.workspace.accumulator(f"attention.qkv/{self.qkv_size}",
-                                                    (STREAMING_MAX_TOKENS, self.qkv_size))
-            project_into_accumulator(x, self.w_qkv, accumulator, n, ctx.status,
-                                     ctx.ordered_sums)
-            self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads, accum=accumulator)
-        elif not self.position.project_and_apply(ctx, cache, x, self.w_qkv, qkv, self.heads,
-                                                 self.kv_heads):
-            project(x, self.w_qkv, qkv, n, ops.EPI_STORE, ctx.status)
-            self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
-
         window = cache.window or 0
         kept = self.keep_first if window else 0
         # prompt portions of at least TENSOR_CORE_MIN_QUERY tokens go to a tensor-core
@@ -323,6 +304,33 @@ class PagedAttention(Mixer):
                                 ctx.status, request_start=ctx.request_start,
                                 skip_query_len=TENSOR_CORE_MIN_QUERY if tensor_cores else 0,
                                 arrivals=arrivals, keep_first=kept)
+
+    def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
+                residual: torch.Tensor) -> None:
+        n = ctx.n_tokens
+        # scratch is named by its width: layers of different sizes each keep their own buffer
+        # (a name whose shape changed from layer to layer would be replaced at every call)
+        qkv = ctx.workspace.get(f"attention.qkv/{self.projected_size}",
+                                (ctx.capacity, self.projected_size), ctx.dtype)
+        context = ctx.workspace.get(f"attention.context/{self.q_size}",
+                                    (ctx.capacity, self.q_size), ctx.dtype)
+        uncleared = gate_rows = None
+        if self.conv_taps > 1:
+            uncleared, gate_rows = self.project_filtered(ctx, cache, x, qkv)
+        elif is_weight_stream(x, self.w_qkv, n):
+            # few tokens: split-K into a float32 accumulator that the rotary kernel reads,
+            # rounds as the product's store would have, and clears
+            accumulator = ctx.workspace.accumulator(f"attention.qkv/{self.qkv_size}",
+                                                    (STREAMING_MAX_TOKENS, self.qkv_size))
+            project_into_accumulator(x, self.w_qkv, accumulator, n, ctx.status,
+                                     ctx.ordered_sums)
+            self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads, accum=accumulator)
+        elif not self.position.project_and_apply(ctx, cache, x, self.w_qkv, qkv, self.heads,
+                                                 self.kv_heads):
+            project(x, self.w_qkv, qkv, n, ops.EPI_STORE, ctx.status)
+            self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
+
+        self.attend(ctx, cache, qkv, context)
         restore = getattr(self.position, "restore_values", None)
         if restore is not None:
             restore(ctx, context, self.heads)
@@ -339,4 +347,167 @@ class PagedAttention(Mixer):
         project(context, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
 
 
+class LatentAttention(PagedAttention):
+    """Attention whose keys and values of all heads are functions of one small latent per
+    token, which is all that is cached.
+
+    Parameters: ``num_heads``, ``head_dim`` (the unrotated query/key coordinates of a head),
+    ``rotated_dim`` (the rotated ones behind them; the rotated key part is one vector shared by
+    all heads), ``value_dim``, ``kv_rank`` (the cached latent), ``q_rank`` (the queries' own
+    latent), ``scale``, ``window`` (None: all earlier keys), ``eps`` (of both latents' RMS
+    norms, which have plain weights), ``rotary`` (``theta``, ``dims``: the leading rotated
+    coordinates that are turned; ``layout`` ``interleaved`` or ``halves``), ``output_gate``
+    (``"sigmoid"`` or None).  Tensors: ``q_down`` ``[q_rank, hidden]``, ``q_norm``
+    ``[q_rank]``, ``q_up`` ``[heads * (head_dim + rotated_dim), q_rank]`` (per head the
+    unrotated rows, then the rotated ones), ``kv_down`` ``[kv_rank + rotated_dim, hidden]``,
+    ``kv_norm`` ``[kv_rank]``, ``k_up`` ``[heads * head_dim, kv_rank]``, ``v_up``
+    ``[heads * value_dim, kv_rank]``, ``g`` ``[heads * value_dim, hidden]``, ``o``
+    ``[hidden, heads * value_dim]``.
+
+    With ``c`` the normed latent and ``r`` the rotated shared part, head ``h`` scores
+    ``(q_h . Uk_h c + rot(qr_h) . rot(r)) * scale = ([Uk_h' q_h | rot(qr_h)] . [c | rot(r)]) *
+    scale``: the keys' up-projection moves to the query's side and every head attends to the
+    ONE cached row ``[c | rot(r)]`` (a cache of one key head of ``kv_rank + rotated_dim``
+    coordinates); the weighted sum of the value rows ``[c]`` is a latent again, and the head's
+    value up-projection ``Uv_h`` follows it.  The attention kernels are those of
+    :class:`PagedAttention`, with one key/value head and rows of ``row_dim``.
+    """
+
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        Mixer.__init__(self, spec, hidden_size)
+        self.heads = int(spec["num_heads"])
+        self.kv_heads = 1
+        self.plain_dim = int(spec["head_dim"])
+        self.rotated_dim = int(spec.get("rotated_dim") or 0)
+        self.value_dim = int(spec.get("value_dim") or self.plain_dim)
+        self.kv_rank = int(spec["kv_rank"])
+        self.q_rank = int(spec["q_rank"])
+        self.scale = float(spec["scale"])
+        window = spec.get("window")
+        self.window: Optional[int] = int(window) if window else None
+        self.keep_first = 0
+        self.eps = float(spec["eps"])
+        rotary = spec.get("rotary") or {}
+        self.rotary_dims = int(rotary.get("dims", self.rotated_dim)) if self.rotated_dim else 0
+        if self.rotary_dims % 2 or self.rotary_dims > self.rotated_dim:
+            raise ValueError("rotary dims must be even and at most rotated_dim")
+        layout = rotary.get("layout", "interleaved")
+        if layout not in ops.ROTARY_LAYOUTS:
+            raise ValueError(f"unknown rotary layout {layout!r}")
+        self.rotary_layout = ops.ROTARY_LAYOUTS[layout]
+        self.theta = float(rotary.get("theta", 10000.0))
+        gate = spec.get("output_gate")
+        if gate not in (None, "sigmoid"):
+            raise ValueError(f"output gate {gate!r} has no kernel; only 'sigmoid'")
+        self.gated = gate is not None
+        self.head_dim = self.kv_rank + self.rotated_dim        # of the one cached key head
+        self.row_dim = row_width(self.head_dim)
+        self.row_dim += self.row_dim % 2                       # the append moves pairs
+        self.q_size = self.heads * self.row_dim
+        self.rows_size = self.q_size + 2 * self.row_dim
+        self.q_width = self.heads * (self.plain_dim + self.rotated_dim)
+        self.o_columns = self.heads * self.value_dim
+        self.down_rows = self.q_rank + self.kv_rank + self.rotated_dim
+        self.names = dict(spec.tensors)
+        self.dtype = torch.float32
+
+    def kv_need(self) -> Optional[KvNeed]:
+        return KvNeed(1, self.row_dim, self.window, 0)
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    @property
+    def graph_safe(self) -> bool:
+        return True
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        h = self.hidden_size
+        requests = [
+            TensorRequest(self.names["q_down"], (self.q_rank, h)),
+            TensorRequest(self.names["q_norm"], (self.q_rank,), role="scale"),
+            TensorRequest(self.names["q_up"], (self.q_width, self.q_rank)),
+            TensorRequest(self.names["kv_down"], (self.kv_rank + self.rotated_dim, h)),
+            TensorRequest(self.names["kv_norm"], (self.kv_rank,), role="scale"),
+            TensorRequest(self.names["k_up"], (self.heads * self.plain_dim, self.kv_rank)),
+            TensorRequest(self.names["v_up"], (self.o_columns, self.kv_rank)),
+            TensorRequest(self.names["o"], (h, self.o_columns)),
+        ]
+        if self.gated:
+            requests.append(TensorRequest(self.names["g"], (self.o_columns, h)))
+        return requests
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        def matrix(value: torch.Tensor) -> torch.Tensor:
+            return value.to(device=device, dtype=dtype).contiguous()
+
+        def scale(role: str) -> torch.Tensor:
+            return tensors[self.names[role]].to(device=device, dtype=torch.float32).contiguous()
+        heads, plain, rotated = self.heads, self.plain_dim, self.rotated_dim
+        self.w_down = Weight(matrix(torch.cat([tensors[self.names["q_down"]],
+                                               tensors[self.names["kv_down"]]], dim=0)))
+        # the queries' up-projection: every head's unrotated rows first, then the rotated ones
+        q_up = tensors[self.names["q_up"]].reshape(heads, plain + rotated, self.q_rank)
+        self.w_q_up = Weight(matrix(torch.cat([q_up[:, :plain].reshape(heads * plain, self.q_rank),
+                                               q_up[:, plain:].reshape(heads * rotated, self.q_rank)],
+                                              dim=0)))
+        # per head [kv_rank, head_dim]: the keys' up-projection, transposed
+        k_up = tensors[self.names["k_up"]].reshape(heads, plain, self.kv_rank)
+        self.w_k_up = matrix(k_up.transpose(1, 2))
+        self.w_v_up = matrix(tensors[self.names["v_up"]].reshape(heads, self.value_dim, self.kv_rank))
+        self.w_o = Weight(matrix(tensors[self.names["o"]]))
+        self.w_g = Weight(matrix(tensors[self.names["g"]])) if self.gated else None
+        self.q_norm, self.kv_norm = scale("q_norm"), scale("kv_norm")
+        self.freq = self.freq_exact = None
+        if self.rotary_dims:
+            exponent = -2.0 * torch.arange(self.rotary_dims // 2, dtype=torch.float64) \
+                / float(self.rotary_dims)
+            exact = torch.pow(torch.tensor(self.theta, dtype=torch.float64), exponent)
+            self.freq_exact = exact.to(device).contiguous()
+            self.freq = exact.to(torch.float32).to(device).contiguous()
+        self._no_angles = torch.zeros((1, 1), dtype=torch.float32, device=device)
+        self.dtype = dtype
+
+    def weight_bytes(self) -> int:
+        held = [self.w_down, self.w_q_up, self.w_o] + ([self.w_g] if self.gated else [])
+        small = self.w_k_up.numel() + self.w_v_up.numel()
+        return sum(weight.nbytes() for weight in held) + small * self.w_k_up.element_size()
+
+    def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
+                residual: torch.Tensor) -> None:
+        n = ctx.n_tokens
+        get = ctx.workspace.get
+        down = get(f"latent.down/{self.down_rows}", (ctx.capacity, self.down_rows), torch.float32)
+        latent = get(f"latent.query_latent/{self.q_rank}", (ctx.capacity, self.q_rank), ctx.dtype)
+        q = get(f"latent.q/{self.q_width}", (ctx.capacity, self.q_width), ctx.dtype)
+        rows = get(f"latent.rows/{self.rows_size}", (ctx.capacity, self.rows_size), ctx.dtype)
+        context = get(f"attention.context/{self.q_size}", (ctx.capacity, self.q_size), ctx.dtype)
+        heads_out = get(f"latent.heads/{self.o_columns}", (ctx.capacity, self.o_columns), ctx.dtype)
+        project(x, self.w_down, down, n, ops.EPI_STORE_F32, ctx.status)
+        ops.latent_prepare(down, self.q_norm, self.kv_norm, self.eps, ctx.positions, self.freq,
+                           self.freq_exact, self.rotary_dims, self.rotary_layout, latent, rows,
+                           self.q_size, n, self.q_rank, self.kv_rank, self.rotated_dim,
+                           self.row_dim)
+        project(latent, self.w_q_up, q, n, ops.EPI_STORE, ctx.status)
+        # [Uk_h' q_h | rot(qr_h) | 0] per head
+        ops.head_products(q, self.plain_dim, self.w_k_up, rows, self.row_dim, n)
+        ops.latent_queries(q, self.heads * self.plain_dim, rows, ctx.positions, self.freq,
+                           self.freq_exact, self.rotary_dims, self.rotary_layout, n, self.heads,
+                           self.kv_rank, self.rotated_dim, self.row_dim)
+        write = cache.owns and cache.keys is not None
+        ops.rope_append(rows, ctx.positions, ctx.token_request, ctx.request_slot,
+                        cache.block_tables, cache.keys if write else None,
+                        cache.values if write else None, self._no_angles, self._no_angles, n,
+                        self.heads, 1, self.row_dim, 0, 0, cache.page_size, cache.num_pages,
+                        ctx.status)
+        self.attend(ctx, cache, rows, context)
+        ops.head_products(context, self.row_dim, self.w_v_up, heads_out, self.value_dim, n)
+        if self.gated:
+            gate = get(f"attention.gate/{self.o_columns}", (ctx.capacity, self.o_columns), ctx.dtype)
+            project(x, self.w_g, gate, n, ops.EPI_STORE, ctx.status)
+            ops.sigmoid_gate(heads_out, gate, n, self.o_columns)
+        project(heads_out, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
+
+
 register_part("mixer", "paged_attention", PagedAttention)
+register_part("mixer", "latent_attention", LatentAttention)

@@ -210,12 +210,14 @@ class FeedForward(Part):
 # ------------------------------------------------------------------- registry
 
 _REGISTRY: Dict[Tuple[str, str], Callable[[PartSpec, int], Part]] = {}
-_FAMILIES = ("norm", "position", "mixer", "feed_forward", "embedding", "lm_head", "connection")
+_FAMILIES = ("norm", "position", "mixer", "feed_forward", "embedding", "lm_head", "connection",
+             "entry")
 
 
 def register_part(family: str, kind: str, factory: Callable[[PartSpec, int], Part]) -> None:
     """Make ``kind`` buildable.  ``family`` is one of norm, position, mixer, feed_forward,
-    embedding, lm_head, connection; ``factory(spec, hidden_size)`` returns the part."""
+    embedding, lm_head, connection, entry (a part run before a schedule entry on the residual
+    and the embedding's output); ``factory(spec, hidden_size)`` returns the part."""
     if family not in _FAMILIES:
         raise ValueError(f"unknown part family {family!r}; known: {', '.join(_FAMILIES)}")
     _REGISTRY[(family, kind)] = factory

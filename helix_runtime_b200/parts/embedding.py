@@ -1,7 +1,8 @@
 """Token embedding and the output head.
 
 Embedding: ``hidden[t] = table[id[t]] * scale`` widened into the float32 residual stream
-(src/model/cpu_llama.cpp:21-27, 49).  Head: ``logits = x @ head.T`` in float32
+(src/model/cpu_llama.cpp:21-27, 49); with the parameter ``norm`` (a norm's part spec) the
+looked-up rows pass that norm, float32 in and out.  Head: ``logits = x @ head.T`` in float32
 (src/model/cpu_llama.cpp:107); when the checkpoint has no head tensor and ties its
 embeddings the table stands in (tools/convert_hf_llama.py:497-510).
 """
@@ -14,7 +15,7 @@ import torch
 from ..config.spec import PartSpec
 from ..ops import library as ops
 from ..weights.loader import TensorRequest
-from .base import Part, StepContext, register_part
+from .base import Part, StepContext, build_part, register_part
 from .linear import Weight, project
 
 
@@ -26,16 +27,29 @@ class TokenEmbedding(Part):
         self.scale = float(spec.get("scale", 1.0))
         self.name = spec.tensors["weight"]
         self.table: Optional[torch.Tensor] = None
+        norm = spec.get("norm")
+        self.norm = None if norm is None else build_part("norm", norm, hidden_size)
 
     def tensor_requests(self) -> List[TensorRequest]:
-        return [TensorRequest(self.name, (self.vocab_size, self.hidden_size), role="embedding")]
+        requests = [TensorRequest(self.name, (self.vocab_size, self.hidden_size), role="embedding")]
+        if self.norm is not None:
+            requests += self.norm.tensor_requests()
+        return requests
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
         self.table = tensors[self.name].to(device=device, dtype=dtype).contiguous()
+        if self.norm is not None:
+            self.norm.bind(tensors, dtype, device)
 
     def forward(self, ctx: StepContext, residual: torch.Tensor) -> None:
-        ops.embed(self.table, ctx.token_ids[:ctx.n_tokens], residual[:ctx.n_tokens], ctx.status,
-                  self.scale)
+        n = ctx.n_tokens
+        if self.norm is None:
+            ops.embed(self.table, ctx.token_ids[:n], residual[:n], ctx.status, self.scale)
+            return
+        looked_up = ctx.workspace.get(f"embedding.rows/{self.hidden_size}",
+                                      (ctx.capacity, self.hidden_size), torch.float32)
+        ops.embed(self.table, ctx.token_ids[:n], looked_up[:n], ctx.status, self.scale)
+        self.norm.forward(ctx, looked_up, residual)     # a float32 output: the norm stores float32
 
 
 class LmHead(Part):

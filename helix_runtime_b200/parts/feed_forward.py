@@ -124,5 +124,71 @@ class DenseMlp(FeedForward):
         project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
 
 
+class RoutedExperts(FeedForward):
+    """``experts`` small gated feed-forwards of which every token uses ``top``, chosen by a
+    router: ``s = sigmoid(R x)`` (float32 sums and scores), the ``top`` largest scores (the
+    lowest index among equals), weights ``s / (sum of the chosen + 1e-20) * scale``, output
+    ``sum_k weight_k * down_k(act(gate_k x) * (up_k x))``.  Parameters: ``experts``, ``top``,
+    ``intermediate_size`` (of one expert), ``scale``, ``activation``.  Tensors: ``router``
+    ``[experts, hidden]`` and, per expert ``e``, ``gate.{e}``, ``up.{e}`` ``[intermediate,
+    hidden]`` and ``down.{e}`` ``[hidden, intermediate]``; at load they are stacked into
+    ``[experts, 2 * intermediate, hidden]`` and ``[experts, hidden, intermediate]``.
+    Nothing is read back to the host, so a step records into a CUDA graph."""
+
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        super().__init__(spec, hidden_size)
+        self.experts = int(spec["experts"])
+        self.top = int(spec["top"])
+        if not 1 <= self.top <= self.experts:
+            raise ValueError("top counts the experts a token uses: between 1 and experts")
+        self.intermediate = int(spec["intermediate_size"])
+        self.scale = float(spec.get("scale", 1.0))
+        activation = spec.get("activation", "silu")
+        if activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} has no kernel; known: "
+                             + ", ".join(sorted(ops.GATE_ACTIVATIONS)))
+        self.activation = ops.GATE_ACTIVATIONS[activation]
+        self.names = dict(spec.tensors)
+        self.w_router: Optional[Weight] = None
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        h, i = self.hidden_size, self.intermediate
+        requests = [TensorRequest(self.names["router"], (self.experts, h))]
+        for e in range(self.experts):
+            requests += [TensorRequest(self.names[f"gate.{e}"], (i, h)),
+                         TensorRequest(self.names[f"up.{e}"], (i, h)),
+                         TensorRequest(self.names[f"down.{e}"], (h, i))]
+        return requests
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        self.w_router = Weight(tensors[self.names["router"]].to(device=device, dtype=dtype)
+                               .contiguous())
+        self.w_gate_up = torch.stack([
+            torch.cat([tensors[self.names[f"gate.{e}"]], tensors[self.names[f"up.{e}"]]], dim=0)
+            for e in range(self.experts)]).to(device=device, dtype=dtype).contiguous()
+        self.w_down = torch.stack([tensors[self.names[f"down.{e}"]] for e in range(self.experts)]) \
+            .to(device=device, dtype=dtype).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.w_router.nbytes() + (self.w_gate_up.numel() + self.w_down.numel()) \
+            * self.w_down.element_size()
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, residual: torch.Tensor) -> None:
+        n = ctx.n_tokens
+        get = ctx.workspace.get
+        sums = get(f"experts.router/{self.experts}", (ctx.capacity, self.experts), torch.float32)
+        chosen = get(f"experts.chosen/{self.top}", (ctx.capacity, self.top), torch.int32)
+        weights = get(f"experts.weights/{self.top}", (ctx.capacity, self.top), torch.float32)
+        act = get(f"experts.act/{self.top}x{self.intermediate}",
+                  (ctx.capacity * self.top, self.intermediate), ctx.dtype)
+        project(x, self.w_router, sums, n, ops.EPI_STORE_F32, ctx.status)
+        ops.route_top(sums, chosen, weights, n, self.experts, self.top, self.scale)
+        ops.expert_gate_up(x, self.w_gate_up, chosen, act, n, self.top, self.activation)
+        ops.expert_down(act, self.w_down, chosen, weights, residual, n, self.top)
+
+
 register_part("feed_forward", "gated_mlp", GatedMlp)
+register_part("feed_forward", "routed_experts", RoutedExperts)
 register_part("feed_forward", "dense_mlp", DenseMlp)

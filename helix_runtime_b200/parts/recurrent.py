@@ -24,6 +24,23 @@ then ``S_t = diag(w_t) S_(t-1) + k_t v_t'``; each head's ``o`` over its root mea
 ``norm``, times the gate, then the output projection.  State: ``h'`` and the
 matrices ``S`` (``ops.scan_state_floats`` floats per head).
 
+:class:`LinearState` (``linear_state``).  Linear attention with one ``[head_dim, value_dim]``
+matrix per head and no softmax.  Parameters ``heads``, ``qk_heads`` (query/key heads; value head
+``h`` reads ``h // (heads / qk_heads)``), ``head_dim``, ``value_dim``, ``rule`` (``decay``:
+``S <- g S + k v'``; ``delta``: ``S <- g S; u = beta (v - S' k); S <- S + k u'``; then
+``o = S' q``), ``decay`` (a list: one constant per head; left out: ``g = exp(-exp(A_log)
+softplus(W_a x + dt_bias))``), ``filter_taps`` (a causal per-channel filter with silu on q, k
+and v), ``unit_norm`` (q and k divided by ``sqrt(sum x^2 + unit_eps)`` per head), ``rotary``
+(``theta``, ``dims``, ``layout``: q and k rotated by their position over their first ``dims``
+coordinates), ``q_scale``, ``k_scale``, ``norm_weight`` (the head norm has a weight
+``[value_dim]`` shared by the heads), ``eps``.  Each head's ``o`` over its root mean square, times
+the weight, times ``silu(W_g x)``, then the output projection.  State: the filter's last inputs
+and the matrices.
+
+:class:`InputFilter` (``input_filter``).  Parameters ``taps``, ``mixer`` (a part spec): the inner
+mixer reads ``x + conv(x)``, ``conv`` a causal per-channel filter over time (tensor ``filter``
+``[hidden, taps]``, the last tap on the token itself); the last ``taps - 1`` inputs are state.
+
 :class:`SideBySide` (``side_by_side``).  Parameters ``mixers`` (part specs) and ``scales``: every
 mixer reads the same input and the result is ``sum_i scales[i] * mixer_i(x)``, summed in float32.
 """
@@ -202,6 +219,214 @@ class TimeMix(Mixer):
                 ctx.ordered_sums)
 
 
+def _flat_state(mixer: Mixer) -> int:
+    """Floats of an inner mixer's state row (0: none); inner mixers keep one float32 row."""
+    need = mixer.state_need()
+    if need is None:
+        return 0
+    if need.dtype != torch.float32 or len(need.shape) != 1:
+        raise ValueError("a mixer inside another keeps its state as one float32 row")
+    return need.shape[0]
+
+
+class LinearState(Mixer):
+    RULES = ("decay", "delta")
+
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        super().__init__(spec, hidden_size)
+        self.heads = int(spec["heads"])
+        self.qk_heads = int(spec.get("qk_heads") or self.heads)
+        self.head_dim = int(spec["head_dim"])
+        self.value_dim = int(spec.get("value_dim") or self.head_dim)
+        self.rule = spec.get("rule", "decay")
+        if self.rule not in self.RULES:
+            raise ValueError(f"unknown rule {self.rule!r}; known: {', '.join(self.RULES)}")
+        if self.heads % self.qk_heads:
+            raise ValueError("heads must be a multiple of qk_heads")
+        decay = spec.get("decay")
+        self.fixed_decay = None if decay is None else [float(value) for value in decay]
+        if self.fixed_decay is not None and len(self.fixed_decay) != self.heads:
+            raise ValueError("a constant decay is given per head")
+        self.taps = int(spec.get("filter_taps") or 1)
+        self.unit_norm = bool(spec.get("unit_norm", False))
+        self.unit_eps = float(spec.get("unit_eps", 1e-6))
+        self.rotary = spec.get("rotary")
+        if self.rotary is not None:
+            dims = int(self.rotary["dims"])
+            if dims % 2 or not 0 <= dims <= self.head_dim:
+                raise ValueError("rotary dims must be even and at most head_dim")
+            if self.rotary.get("layout", "halves") not in ops.ROTARY_LAYOUTS:
+                raise ValueError(f"unknown rotary layout {self.rotary.get('layout')!r}")
+        self.q_scale = float(spec.get("q_scale", 1.0))
+        self.k_scale = float(spec.get("k_scale", 1.0))
+        self.norm_weight = bool(spec.get("norm_weight", False))
+        self.eps = float(spec["eps"])
+        self.qk_width = self.qk_heads * self.head_dim
+        self.v_width = self.heads * self.value_dim
+        self.filtered = 2 * self.qk_width + self.v_width
+        # projected rows: q | k | v | gate | beta (delta) | decay input (learned decay)
+        self.gate_at = self.filtered
+        self.beta_at = self.gate_at + self.v_width
+        self.decay_at = self.beta_at + (self.heads if self.rule == "delta" else 0)
+        self.projected = self.decay_at + (self.heads if self.fixed_decay is None else 0)
+        self.filter_state = (self.taps - 1) * self.filtered
+        self.matrix_state = self.heads * ops.scan_state_floats(self.value_dim, self.head_dim)
+        self.names = dict(spec.tensors)
+        self.w_in: Optional[Weight] = None
+        self.w_o: Optional[Weight] = None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return StateNeed((self.filter_state + self.matrix_state,), torch.float32)
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        h = self.hidden_size
+        requests = [TensorRequest(self.names["q"], (self.qk_width, h)),
+                    TensorRequest(self.names["k"], (self.qk_width, h)),
+                    TensorRequest(self.names["v"], (self.v_width, h)),
+                    TensorRequest(self.names["g"], (self.v_width, h)),
+                    TensorRequest(self.names["o"], (h, self.v_width))]
+        if self.rule == "delta":
+            requests.append(TensorRequest(self.names["beta"], (self.heads, h)))
+        if self.fixed_decay is None:
+            requests += [TensorRequest(self.names["decay"], (self.heads, h)),
+                         TensorRequest(self.names["a_log"], (self.heads,), role="scale"),
+                         TensorRequest(self.names["dt_bias"], (self.heads,), role="scale")]
+        if self.taps > 1:
+            requests += [TensorRequest(self.names[f"{part}_filter"], (rows, self.taps), role="scale")
+                         for part, rows in (("q", self.qk_width), ("k", self.qk_width),
+                                            ("v", self.v_width))]
+        if self.norm_weight:
+            requests.append(TensorRequest(self.names["norm"], (self.value_dim,), role="scale"))
+        return requests
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        def scale(role: str) -> torch.Tensor:
+            return tensors[self.names[role]].to(device=device, dtype=torch.float32).contiguous()
+        fused = [tensors[self.names[role]] for role in ("q", "k", "v", "g")]
+        if self.rule == "delta":
+            fused.append(tensors[self.names["beta"]])
+        if self.fixed_decay is None:
+            fused.append(tensors[self.names["decay"]])
+        self.w_in = Weight(torch.cat(fused, dim=0).to(device=device, dtype=dtype).contiguous())
+        self.w_o = Weight(tensors[self.names["o"]].to(device=device, dtype=dtype).contiguous())
+        self.a_log = self.dt_bias = self.decay = self.decay_m1 = None
+        if self.fixed_decay is None:
+            self.a_log, self.dt_bias = scale("a_log"), scale("dt_bias")
+        else:
+            exact = torch.tensor(self.fixed_decay, dtype=torch.float64)
+            self.decay = exact.to(torch.float32).to(device)
+            self.decay_m1 = (exact - 1.0).to(torch.float32).to(device)
+        self.filter = None
+        if self.taps > 1:
+            self.filter = torch.cat([scale("q_filter"), scale("k_filter"), scale("v_filter")],
+                                    dim=0).contiguous()
+        weight = scale("norm") if self.norm_weight else \
+            torch.ones((self.value_dim,), dtype=torch.float32, device=device)
+        self.norm = weight.repeat(self.heads).contiguous()
+        self.freq = self.freq_exact = None
+        self.rotary_dims, self.rotary_layout = 0, 1
+        if self.rotary is not None and int(self.rotary["dims"]) > 0:
+            dims = int(self.rotary["dims"])
+            exponent = -2.0 * torch.arange(dims // 2, dtype=torch.float64) / float(dims)
+            exact = torch.pow(torch.tensor(float(self.rotary["theta"]), dtype=torch.float64),
+                              exponent)
+            self.freq_exact = exact.to(device).contiguous()
+            self.freq = exact.to(torch.float32).to(device).contiguous()
+            self.rotary_dims = dims
+            self.rotary_layout = ops.ROTARY_LAYOUTS[self.rotary.get("layout", "halves")]
+
+    def weight_bytes(self) -> int:
+        return self.w_in.nbytes() + self.w_o.nbytes()
+
+    def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
+                residual: torch.Tensor) -> None:
+        n = ctx.n_tokens
+        wide = -(-self.projected // 8) * 8
+        rows = ctx.workspace.get(f"linear_state.rows/{wide}", (ctx.capacity, wide), ctx.dtype)
+        o = ctx.workspace.get(f"linear_state.o/{self.v_width}", (ctx.capacity, self.v_width),
+                              torch.float32)
+        gated = ctx.workspace.get(f"linear_state.gated/{self.v_width}",
+                                  (ctx.capacity, self.v_width), ctx.dtype)
+        project(x, self.w_in, rows, n, ops.EPI_STORE, ctx.status)
+        qkv = rows
+        if self.taps > 1:
+            qkv = ctx.workspace.get(f"linear_state.filtered/{self.filtered}",
+                                    (ctx.capacity, self.filtered), ctx.dtype)
+            ops.causal_filter(rows[:, :self.filtered], qkv, self.filter, None,
+                              _state_piece(cache, 0, self.filter_state), n, True,
+                              ctx.token_request, ctx.request_slot, ctx.request_start)
+        learned = self.fixed_decay is None
+        ops.linear_state_scan(
+            qkv[:, :self.qk_width], qkv[:, self.qk_width:2 * self.qk_width],
+            qkv[:, 2 * self.qk_width:self.filtered],
+            _state_piece(cache, self.filter_state, self.matrix_state), o, ctx.request_start,
+            ctx.request_slot, ctx.n_requests, self.heads, self.qk_heads, self.head_dim,
+            self.value_dim, delta=self.rule == "delta",
+            decay_in=rows[:, self.decay_at:self.decay_at + self.heads] if learned else None,
+            beta_in=rows[:, self.beta_at:self.beta_at + self.heads] if self.rule == "delta" else None,
+            a_log=self.a_log, dt_bias=self.dt_bias, fixed_decay=self.decay,
+            fixed_decay_m1=self.decay_m1,
+            positions=ctx.positions if self.rotary_dims else None, freq=self.freq,
+            freq_exact=self.freq_exact, rotary_dim=self.rotary_dims,
+            rotary_layout=self.rotary_layout, unit_norm=self.unit_norm, unit_eps=self.unit_eps,
+            q_scale=self.q_scale, k_scale=self.k_scale, tokens=n)
+        ops.gated_group_norm(o, rows[:, self.gate_at:self.gate_at + self.v_width], self.norm, gated,
+                             n, self.heads, self.eps, gate_after=True)
+        project(gated, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
+
+
+class InputFilter(Mixer):
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        super().__init__(spec, hidden_size)
+        self.taps = int(spec["taps"])
+        if self.taps < 1:
+            raise ValueError("taps counts the filter's taps: at least 1")
+        self.inner: Mixer = build_part("mixer", spec["mixer"], hidden_size)
+        self.own_state = (self.taps - 1) * hidden_size
+        self.inner_state = _flat_state(self.inner)
+        self.name = spec.tensors["filter"]
+        self.filter: Optional[torch.Tensor] = None
+
+    @property
+    def graph_safe(self) -> bool:
+        return self.inner.graph_safe
+
+    def kv_need(self) -> Optional[KvNeed]:
+        return self.inner.kv_need()
+
+    def state_need(self) -> Optional[StateNeed]:
+        total = self.own_state + self.inner_state
+        return StateNeed((total,), torch.float32) if total else None
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        return [TensorRequest(self.name, (self.hidden_size, self.taps), role="scale"),
+                *self.inner.tensor_requests()]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        taps = tensors[self.name].to(device=device, dtype=torch.float32).clone()
+        taps[:, -1] += 1.0          # x + conv(x): the token's own tap carries the identity
+        self.filter = taps.contiguous()
+        self.inner.bind(tensors, dtype, device)
+
+    def weight_bytes(self) -> int:
+        return self.filter.numel() * 4 + self.inner.weight_bytes()
+
+    def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
+                residual: torch.Tensor) -> None:
+        filtered = ctx.workspace.get(f"input_filter.rows/{self.hidden_size}",
+                                     (ctx.capacity, self.hidden_size), ctx.dtype)
+        ops.causal_filter(x, filtered, self.filter, None,
+                          _state_piece(cache, 0, self.own_state) if self.taps > 1 else None,
+                          ctx.n_tokens, False, ctx.token_request, ctx.request_slot,
+                          ctx.request_start)
+        view = cache
+        if cache.state is not None:
+            view = dataclasses.replace(
+                cache, state=cache.state[:, self.own_state:self.own_state + self.inner_state]
+                if self.inner_state else None)
+        self.inner.forward(ctx, view, filtered, residual)
+
+
 class SideBySide(Mixer):
     def __init__(self, spec: PartSpec, hidden_size: int) -> None:
         super().__init__(spec, hidden_size)
@@ -267,3 +492,5 @@ class SideBySide(Mixer):
 register_part("mixer", "state_space", StateSpaceMixer)
 register_part("mixer", "time_mix", TimeMix)
 register_part("mixer", "side_by_side", SideBySide)
+register_part("mixer", "linear_state", LinearState)
+register_part("mixer", "input_filter", InputFilter)
