@@ -247,7 +247,12 @@ class LinearState(Mixer):
         self.fixed_decay = None if decay is None else [float(value) for value in decay]
         if self.fixed_decay is not None and len(self.fixed_decay) != self.heads:
             raise ValueError("a constant decay is given per head")
-        self.taps = int(spec.get("filter_taps") or 1)
+        # None: q, k and v go into the recurrence as projected; a count (1 too): a causal filter
+        # of that many taps and silu come first
+        taps = spec.get("filter_taps")
+        self.taps = None if taps is None else int(taps)
+        if self.taps is not None and self.taps < 1:
+            raise ValueError("filter_taps counts the filter's taps: at least 1")
         self.unit_norm = bool(spec.get("unit_norm", False))
         self.unit_eps = float(spec.get("unit_eps", 1e-6))
         self.rotary = spec.get("rotary")
@@ -269,7 +274,7 @@ class LinearState(Mixer):
         self.beta_at = self.gate_at + self.v_width
         self.decay_at = self.beta_at + (self.heads if self.rule == "delta" else 0)
         self.projected = self.decay_at + (self.heads if self.fixed_decay is None else 0)
-        self.filter_state = (self.taps - 1) * self.filtered
+        self.filter_state = ((self.taps or 1) - 1) * self.filtered
         self.matrix_state = self.heads * ops.scan_state_floats(self.value_dim, self.head_dim)
         self.names = dict(spec.tensors)
         self.w_in: Optional[Weight] = None
@@ -291,7 +296,7 @@ class LinearState(Mixer):
             requests += [TensorRequest(self.names["decay"], (self.heads, h)),
                          TensorRequest(self.names["a_log"], (self.heads,), role="scale"),
                          TensorRequest(self.names["dt_bias"], (self.heads,), role="scale")]
-        if self.taps > 1:
+        if self.taps is not None:
             requests += [TensorRequest(self.names[f"{part}_filter"], (rows, self.taps), role="scale")
                          for part, rows in (("q", self.qk_width), ("k", self.qk_width),
                                             ("v", self.v_width))]
@@ -317,7 +322,7 @@ class LinearState(Mixer):
             self.decay = exact.to(torch.float32).to(device)
             self.decay_m1 = (exact - 1.0).to(torch.float32).to(device)
         self.filter = None
-        if self.taps > 1:
+        if self.taps is not None:
             self.filter = torch.cat([scale("q_filter"), scale("k_filter"), scale("v_filter")],
                                     dim=0).contiguous()
         weight = scale("norm") if self.norm_weight else \
@@ -349,11 +354,12 @@ class LinearState(Mixer):
                                   (ctx.capacity, self.v_width), ctx.dtype)
         project(x, self.w_in, rows, n, ops.EPI_STORE, ctx.status)
         qkv = rows
-        if self.taps > 1:
+        if self.taps is not None:
             qkv = ctx.workspace.get(f"linear_state.filtered/{self.filtered}",
                                     (ctx.capacity, self.filtered), ctx.dtype)
             ops.causal_filter(rows[:, :self.filtered], qkv, self.filter, None,
-                              _state_piece(cache, 0, self.filter_state), n, True,
+                              _state_piece(cache, 0, self.filter_state) if self.taps > 1 else None,
+                              n, True,
                               ctx.token_request, ctx.request_slot, ctx.request_start)
         learned = self.fixed_decay is None
         ops.linear_state_scan(
