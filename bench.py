@@ -404,6 +404,38 @@ def zuzadra_config(shape: dict, options):
                          layers=layers, streams=4, max_positions=shape["max_position_embeddings"])
 
 
+def medolorn_config(shape: dict, options):
+    """The Medolorn design with the layer sizes of a Llama shape: the same width, vocabulary and
+    active feed-forward size (16 routed experts of a quarter of the shape's feed-forward each,
+    every token using 4).  Layers in turn: the gated delta rule (heads of 128, half as many
+    query/key heads, filters of four taps), latent attention twice (the shape's heads, 128
+    unrotated and 64 rotated coordinates, a cached row of 192 + 64, queries through a latent
+    of a quarter of the width, window ``--window``), retention (the shape's heads).  An input
+    filter of four taps and gated connections in every layer; no repeated stretch."""
+    import math
+
+    from helix_runtime_b200.config.medolorn import (DeltaMixerConfig, LatentAttentionConfig,
+                                                    MedolornConfig, MedolornLayerConfig,
+                                                    RetentionMixerConfig, RoutedMlpConfig)
+    heads, dim, width = shape["num_attention_heads"], shape["head_dim"], shape["hidden_size"]
+    ff = -(-shape["intermediate_size"] // 4 // 128) * 128
+    mlp = RoutedMlpConfig(ff=ff, experts=16, top=4, scale=1.0)
+    delta = DeltaMixerConfig(heads=heads, kv_heads=max(1, heads // 2), dim=dim, vdim=dim, conv=4)
+    latent = LatentAttentionConfig(heads=heads, dim=dim, rot_dim=64, vdim=dim, kv_rank=192,
+                                   q_rank=width // 4, scale=1.0 / math.sqrt(dim + 64),
+                                   window=options.window or 1024, rot_base=500000.0, rot_dims=64)
+    retention = RetentionMixerConfig(heads=heads, dim=dim, vdim=dim,
+                                     decay=tuple(1.0 - 2.0 ** (-5 - index % 6) for index in range(heads)),
+                                     rot_base=1000000.0, rot_dims=dim)
+    kinds = (("delta", delta), ("latent_attention", latent), ("latent_attention", latent),
+             ("retention", retention))
+    layers = tuple(MedolornLayerConfig(*kinds[index % 4], mlp)
+                   for index in range(shape["num_hidden_layers"]))
+    return MedolornConfig(vocab=shape["vocab_size"], width=width, norm_eps=shape["rms_norm_eps"],
+                          canon_taps=4, layers=layers,
+                          max_positions=shape["max_position_embeddings"])
+
+
 def compare_designs(options, peaks, device) -> int:
     """``--compare``: the Rekasun design beside the Llama design at equal layer sizes
     (``--compare zuzadra``: and the Zuzadra design beside both), a few
@@ -495,8 +527,10 @@ def compare_designs(options, peaks, device) -> int:
         row = {"hidden": shape["hidden_size"], "heads": shape["num_attention_heads"],
                "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"]}
         designs = [("llama", LlamaConfig(**shape)), ("rekasun", rekasun_config(shape, options))]
-        if options.compare == "zuzadra":
+        if options.compare in ("zuzadra", "medolorn"):
             designs.append(("zuzadra", zuzadra_config(shape, options)))
+        if options.compare == "medolorn":
+            designs.append(("medolorn", medolorn_config(shape, options)))
         for design, config in designs:
             model = random_model(config, seed=0, dtype="bfloat16", device=device)
             row[design] = measure(model)
@@ -504,8 +538,9 @@ def compare_designs(options, peaks, device) -> int:
             torch.cuda.empty_cache()
         shapes[name] = row
     print(json.dumps({
-        "metric": "prefill and decode throughput, " + ("Zuzadra and " if options.compare == "zuzadra"
-                                                        else "") +
+        "metric": "prefill and decode throughput, " + {"zuzadra": "Zuzadra and ",
+                                                        "medolorn": "Medolorn, Zuzadra and "}
+                  .get(options.compare, "") +
                   "Rekasun design beside Llama design (bf16)",
         "layers": layers, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
         "rekasun": {"window": options.window, "keep_first": options.keep_first,
@@ -539,15 +574,16 @@ def main() -> int:
     parser.add_argument("--shape", choices=tuple(SHAPES), default="llama-2-7b",
                         help="layer sizes for --serving, --profile and --timeline (the contract "
                              "line is always the Llama-2-7B shape)")
-    parser.add_argument("--design", choices=("llama", "rekasun", "zuzadra"), default="llama",
+    parser.add_argument("--design", choices=("llama", "rekasun", "zuzadra", "medolorn"), default="llama",
                         help="which decoder the layers of --shape are built as, for --profile "
                              "and --timeline (the contract line is always the Llama design)")
     parser.add_argument("--compare", nargs="?", const="rekasun", default=None,
-                        choices=("rekasun", "zuzadra"),
+                        choices=("rekasun", "zuzadra", "medolorn"),
                         help="prefill and decode throughput of the Rekasun design beside the "
                              "Llama design at equal layer sizes (a few layers of each --shape), "
                              "as one JSON line of its own; '--compare zuzadra' adds the Zuzadra "
-                             "design as a third row")
+                             "design as a third row, '--compare medolorn' the Medolorn design "
+                             "as a fourth")
     parser.add_argument("--window", type=int, default=1024,
                         help="--design rekasun / --compare: keys a position sees behind itself")
     parser.add_argument("--keep-first", type=int, default=64,
@@ -604,6 +640,8 @@ def main() -> int:
         config = rekasun_config(shape, options)
     elif options.design == "zuzadra":
         config = zuzadra_config(shape, options)
+    elif options.design == "medolorn":
+        config = medolorn_config(shape, options)
     model = random_model(config, seed=0, dtype="bfloat16", device=device)
     rng = np.random.default_rng(0)
     out_dir = options.log_dir or tempfile.mkdtemp(prefix="helix_bench_")

@@ -134,6 +134,11 @@ struct GemmArgs {
   int k_tiles;        // > 0: the weights are stored as tiles, this many along k
   int* status;
   int activation;     // gated epilogue: what the gate passes through (HxGateActivation)
+  // Grouped product: token tile t multiplies with the rows of group tile_group[t] of the
+  // weight matrix (group g's rows start at g * group_rows); a negative group skips the tile.
+  // The list lies in device memory and is written by an earlier kernel of the stream.
+  const int* tile_group = nullptr;
+  int group_rows = 0;
 };
 
 template <int BN, int EPI>
@@ -162,7 +167,15 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
   const int total_k_blocks = (args.depth + BK - 1) / BK;
   const int kb_begin = blockIdx.z * args.k_blocks_per_split;
   const int kb_end = min(kb_begin + args.k_blocks_per_split, total_k_blocks);
-  const int n_k_blocks = kb_end - kb_begin;
+  int weight_row0 = feature0;      // row of the weight matrix that feature0 is
+  bool skipped = false;
+  if (args.tile_group != nullptr) {
+    hx_pdl_wait();                 // the list is the work of a kernel before this one
+    const int group = args.tile_group[blockIdx.x];
+    skipped = group < 0;
+    weight_row0 = (skipped ? 0 : group * args.group_rows) + feature0;
+  }
+  const int n_k_blocks = skipped ? 0 : kb_end - kb_begin;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -190,10 +203,10 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
         for (int i = 0; i < eager; ++i) {
           uint8_t* stage = smem + i * Config::kStageBytes;
           mbar_expect_tx(&full_bar[i], Config::kStageBytes);
-          load_weight_box(stage, &map_w, &full_bar[i], feature0, kb_begin + i, args.k_tiles);
+          load_weight_box(stage, &map_w, &full_bar[i], weight_row0, kb_begin + i, args.k_tiles);
           if (DUAL)
             load_weight_box(stage + BM * BK * 2, &map_w, &full_bar[i],
-                            args.up_row_offset + feature0, kb_begin + i, args.k_tiles);
+                            args.up_row_offset + weight_row0, kb_begin + i, args.k_tiles);
         }
         hx_pdl_wait();
         for (int i = 0; i < eager; ++i) {
@@ -211,10 +224,10 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
           uint8_t* stage = smem + s * Config::kStageBytes;
           mbar_expect_tx(&full_bar[s], Config::kStageBytes);
           const int k = (kb_begin + i) * BK;
-          load_weight_box(stage, &map_w, &full_bar[s], feature0, kb_begin + i, args.k_tiles);
+          load_weight_box(stage, &map_w, &full_bar[s], weight_row0, kb_begin + i, args.k_tiles);
           if (DUAL)
             load_weight_box(stage + BM * BK * 2, &map_w, &full_bar[s],
-                            args.up_row_offset + feature0, kb_begin + i, args.k_tiles);
+                            args.up_row_offset + weight_row0, kb_begin + i, args.k_tiles);
           tma_load_2d(stage + Config::kWeightBytes, &map_x, &full_bar[s], k, token0);
         }
       }
@@ -1060,6 +1073,67 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
   }
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_gemm_tc");
+  return HX_OK;
+}
+
+// The grouped product: rows of x come in tiles of `token_tile` (16, 32, 64, 128 or 256), and
+// tile t multiplies with group tile_group[t] of w, which holds `groups` matrices of
+// `group_rows` rows one below the other (row-major, row stride ldw); a negative entry skips the
+// tile.  tile_group (device memory, ceil(tokens / token_tile) entries) may be written by the
+// kernel before this one on the stream.  `tokens` is the host's bound on the rows in use; rows
+// of tiles that are only partly in use are computed and stored like the others.  Epilogues 0,
+// 1 and 3 (5); `features` and `up_row_offset` count inside a group.
+HX_API int hx_gemm_tc_grouped(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                              int group_rows, int groups, void* out, int ldo, int tokens,
+                              int features, int depth, int epilogue, int up_row_offset,
+                              int token_tile, const int* tile_group, int* status,
+                              cudaStream_t stream) {
+  int activation = HX_GATE_SILU;
+  if (epilogue == 5) {
+    epilogue = EPI_SWIGLU;
+    activation = HX_GATE_GELU_TANH;
+  }
+  HX_REQUIRE(groups > 0 && group_rows > 0 && tile_group != nullptr,
+             "hx_gemm_tc_grouped: bad groups");
+  HX_REQUIRE(static_cast<long long>(groups) * group_rows < (1ll << 31),
+             "hx_gemm_tc_grouped: too many weight rows");
+  HX_REQUIRE(hx_gemm_tc_supports(tokens, features, depth, ldx, ldw),
+             "hx_gemm_tc_grouped: shape tokens=%d features=%d depth=%d ldx=%d ldw=%d is not "
+             "supported (depth and strides must be multiples of 8)", tokens, features, depth, ldx,
+             ldw);
+  HX_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+             "hx_gemm_tc_grouped: operands must be 16-byte aligned");
+  HX_REQUIRE(x_capacity_rows >= tokens, "hx_gemm_tc_grouped: buffer rows %d < tokens %d",
+             x_capacity_rows, tokens);
+  HX_REQUIRE(status != nullptr, "hx_gemm_tc_grouped: status word missing");
+  HX_REQUIRE(epilogue == EPI_STORE_BF16 || epilogue == EPI_STORE_F32 || epilogue == EPI_SWIGLU,
+             "hx_gemm_tc_grouped: epilogue %d is not one of store and gated", epilogue);
+  HX_REQUIRE(epilogue == EPI_SWIGLU ? up_row_offset + features <= group_rows
+                                    : features <= group_rows,
+             "hx_gemm_tc_grouped: features exceed a group's rows");
+  HX_REQUIRE(ldo >= features, "hx_gemm_tc_grouped: output stride too small");
+  HX_REQUIRE(token_tile == 16 || token_tile == 32 || token_tile == 64 || token_tile == 128 ||
+                 token_tile == 256,
+             "hx_gemm_tc_grouped: token tile %d", token_tile);
+  CUtensorMap map_w, map_x;
+  int rc = get_tensor_map(w, static_cast<uint64_t>(groups) * group_rows, depth, ldw, BM, &map_w);
+  if (rc != HX_OK) return rc;
+  rc = get_tensor_map(x, x_capacity_rows, depth, ldx, token_tile, &map_x);
+  if (rc != HX_OK) return rc;
+  const int total_k_blocks = (depth + BK - 1) / BK;
+  GemmArgs args{out, ldo, tokens, features, depth, up_row_offset, total_k_blocks, 0, status,
+                activation, tile_group, group_rows};
+  const dim3 grid((tokens + token_tile - 1) / token_tile, (features + BM - 1) / BM, 1);
+  HX_REQUIRE(grid.y <= 65535, "hx_gemm_tc_grouped: too many features (%d)", features);
+  switch (token_tile) {
+    case 16: rc = launch_epilogue<16>(epilogue, map_w, map_x, args, grid, stream); break;
+    case 32: rc = launch_epilogue<32>(epilogue, map_w, map_x, args, grid, stream); break;
+    case 64: rc = launch_epilogue<64>(epilogue, map_w, map_x, args, grid, stream); break;
+    case 128: rc = launch_epilogue<128>(epilogue, map_w, map_x, args, grid, stream); break;
+    default: rc = launch_epilogue<256>(epilogue, map_w, map_x, args, grid, stream); break;
+  }
+  if (rc != HX_OK) return rc;
+  HX_CHECK_LAUNCH("hx_gemm_tc_grouped");
   return HX_OK;
 }
 

@@ -183,6 +183,114 @@ __global__ __launch_bounds__(EXPERT_WARPS * 32) void expert_down_kernel(
   }
 }
 
+// ---- the pairs of a step sorted by expert, for one grouped product per projection ----------
+//
+// With many tokens an expert's matrices should be read once for all of its tokens, not once
+// per token.  The (token, choice) pairs are laid out expert by expert, every expert's rows
+// rounded up to a whole tile of the product's token side, the tokens' inputs are copied into
+// that order, two grouped tensor-core products run over the tiles (each tile names its
+// expert), and the outputs are summed back per token in the order of its choices.  A row's
+// result does not depend on where in a tile it lies, so pairs take their rows by atomic
+// counters; rows of padding hold whatever the buffer held and are never read back.
+
+constexpr int ROWS_THREADS = 1024;
+
+// One CTA.  pair_row[pair]: the pair's row in the grouped order (-1: no valid expert);
+// tile_group[t], t < max_tiles: the expert of tile t, -1 behind the last tile in use.
+__global__ __launch_bounds__(ROWS_THREADS) void expert_rows_kernel(
+    const int* __restrict__ chosen, int pairs, int experts, int tile, int max_tiles,
+    int* __restrict__ pair_row, int* __restrict__ tile_group) {
+  extern __shared__ int shared_counts[];
+  int* counts = shared_counts;              // pairs of the expert, then its fill cursor
+  int* first_row = shared_counts + experts; // the expert's first row
+  __shared__ int tiles_in_use;
+  hx_pdl_prologue();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int pair = threadIdx.x; pair < pairs; pair += blockDim.x) {
+    const int e = chosen[pair];
+    if (e >= 0 && e < experts) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int row = 0;
+    for (int e = 0; e < experts; ++e) {
+      first_row[e] = row;
+      row += (counts[e] + tile - 1) / tile * tile;
+    }
+    tiles_in_use = row / tile;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int begin = first_row[e] / tile;
+    const int end = begin + (counts[e] + tile - 1) / tile;
+    for (int t = begin; t < end && t < max_tiles; ++t) tile_group[t] = e;
+  }
+  for (int t = tiles_in_use + threadIdx.x; t < max_tiles; t += blockDim.x) tile_group[t] = -1;
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int pair = threadIdx.x; pair < pairs; pair += blockDim.x) {
+    const int e = chosen[pair];
+    pair_row[pair] = (e >= 0 && e < experts) ? first_row[e] + atomicAdd(&counts[e], 1) : -1;
+  }
+}
+
+// grid (pairs): grouped[pair_row[pair]] = x[pair / top]
+template <typename T>
+__global__ __launch_bounds__(128) void expert_gather_kernel(
+    const T* __restrict__ x, int ld_x, const int* __restrict__ pair_row, T* __restrict__ grouped,
+    int ld_grouped, int top, int width) {
+  hx_pdl_prologue();
+  const int pair = blockIdx.x;
+  const int row = pair_row[pair];
+  if (row < 0) return;
+  const T* from = x + static_cast<size_t>(pair / top) * ld_x;
+  T* to = grouped + static_cast<size_t>(row) * ld_grouped;
+  constexpr int PER = 16 / sizeof(T);
+  if (width % PER == 0 && ld_x % PER == 0 && ld_grouped % PER == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(grouped)) & 15) == 0) {
+    for (int c = threadIdx.x; c < width / PER; c += blockDim.x)
+      reinterpret_cast<uint4*>(to)[c] = reinterpret_cast<const uint4*>(from)[c];
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) to[c] = from[c];
+  }
+}
+
+// grid (ceil(width / 512), tokens): out[t][c] += sum_k weights[t][k] * y[pair_row[t top + k]][c]
+__global__ __launch_bounds__(128) void expert_combine_kernel(
+    const float* __restrict__ y, int ld_y, const int* __restrict__ pair_row,
+    const float* __restrict__ weights, float* __restrict__ out, int ld_out, int top, int width) {
+  hx_pdl_prologue();
+  const int token = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= width) return;
+  float* o = out + static_cast<size_t>(token) * ld_out;
+  const bool wide = c + 4 <= width && ld_y % 4 == 0 && ld_out % 4 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  for (int k = 0; k < top; ++k) {
+    const int row = pair_row[token * top + k];
+    if (row < 0) continue;
+    const float weight = weights[token * top + k];
+    const float* from = y + static_cast<size_t>(row) * ld_y + c;
+    if (wide) {
+      const float4 v = *reinterpret_cast<const float4*>(from);
+      sums[0] = fmaf(weight, v.x, sums[0]); sums[1] = fmaf(weight, v.y, sums[1]);
+      sums[2] = fmaf(weight, v.z, sums[2]); sums[3] = fmaf(weight, v.w, sums[3]);
+    } else {
+      for (int i = 0; i < 4 && c + i < width; ++i) sums[i] = fmaf(weight, from[i], sums[i]);
+    }
+  }
+  if (wide) {
+    float4 v = *reinterpret_cast<float4*>(o + c);
+    v.x += sums[0]; v.y += sums[1]; v.z += sums[2]; v.w += sums[3];
+    *reinterpret_cast<float4*>(o + c) = v;
+  } else {
+    for (int i = 0; i < 4 && c + i < width; ++i) o[c + i] += sums[i];
+  }
+}
+
 }  // namespace
 
 // sums float32 [tokens, ld] (the router's products); chosen int32 and weights float32
@@ -251,5 +359,65 @@ HX_API int hx_expert_down(const void* act, const void* down, const int* chosen,
     HX_REQUIRE(false, "hx_expert_down: unknown dtype %d", dtype);
   }
   HX_CHECK_LAUNCH("hx_expert_down");
+  return HX_OK;
+}
+
+// Tiles the grouped order of `pairs` pairs over `experts` experts can take with this tile.
+HX_API int hx_expert_tile_bound(int pairs, int experts, int tile) {
+  if (pairs < 0 || experts <= 0 || tile <= 0) return 0;
+  return static_cast<int>((static_cast<long long>(pairs) + static_cast<long long>(experts) * (tile - 1) +
+                           tile - 1) / tile);
+}
+
+// chosen int32 [pairs]; pair_row int32 [pairs]; tile_group int32 [max_tiles] with max_tiles at
+// least hx_expert_tile_bound(pairs, experts, tile).
+HX_API int hx_expert_rows(const int* chosen, int pairs, int experts, int tile, int max_tiles,
+                          int* pair_row, int* tile_group, cudaStream_t stream) {
+  HX_REQUIRE(pairs >= 0 && experts > 0 && tile > 0, "hx_expert_rows: bad sizes");
+  HX_REQUIRE(experts <= 4096, "hx_expert_rows: at most 4096 experts");
+  HX_REQUIRE(max_tiles >= hx_expert_tile_bound(pairs, experts, tile),
+             "hx_expert_rows: %d tiles do not hold %d pairs of %d experts", max_tiles, pairs,
+             experts);
+  if (pairs == 0) return HX_OK;
+  hx_launch(expert_rows_kernel, dim3(1), ROWS_THREADS, 2 * experts * sizeof(int), stream, chosen,
+            pairs, experts, tile, max_tiles, pair_row, tile_group);
+  HX_CHECK_LAUNCH("hx_expert_rows");
+  return HX_OK;
+}
+
+// x [tokens, ld_x] and grouped [rows, ld_grouped] in the compute dtype.
+HX_API int hx_expert_gather(const void* x, int ld_x, const int* pair_row, void* grouped,
+                            int ld_grouped, int dtype, int tokens, int top, int width,
+                            cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && top > 0 && width > 0 && ld_x >= width && ld_grouped >= width,
+             "hx_expert_gather: bad sizes");
+  if (tokens == 0) return HX_OK;
+  if (dtype == HX_F32) {
+    hx_launch(expert_gather_kernel<float>, dim3(tokens * top), 128, 0, stream,
+              static_cast<const float*>(x), ld_x, pair_row, static_cast<float*>(grouped),
+              ld_grouped, top, width);
+  } else if (dtype == HX_BF16) {
+    hx_launch(expert_gather_kernel<__nv_bfloat16>, dim3(tokens * top), 128, 0, stream,
+              static_cast<const __nv_bfloat16*>(x), ld_x, pair_row,
+              static_cast<__nv_bfloat16*>(grouped), ld_grouped, top, width);
+  } else {
+    HX_REQUIRE(false, "hx_expert_gather: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_expert_gather");
+  return HX_OK;
+}
+
+// y float32 [rows, ld_y] (an expert's output per grouped row); out float32 [tokens, ld_out] is
+// summed into, a token's choices in ascending order, one writer per element.
+HX_API int hx_expert_combine(const float* y, int ld_y, const int* pair_row, const float* weights,
+                             float* out, int ld_out, int tokens, int top, int width,
+                             cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && top > 0 && width > 0 && ld_y >= width && ld_out >= width,
+             "hx_expert_combine: bad sizes");
+  HX_REQUIRE(tokens <= 65535, "hx_expert_combine: at most 65535 tokens a step");
+  if (tokens == 0) return HX_OK;
+  hx_launch(expert_combine_kernel, dim3((width + 511) / 512, tokens), 128, 0, stream, y, ld_y,
+            pair_row, weights, out, ld_out, top, width);
+  HX_CHECK_LAUNCH("hx_expert_combine");
   return HX_OK;
 }

@@ -175,6 +175,18 @@ def _declare(library: ctypes.CDLL) -> None:
                                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
     library.hx_expert_down.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                        _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_expert_tile_bound.argtypes = [_c_int, _c_int, _c_int]
+    library.hx_expert_rows.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_expert_gather.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                         _c_int, _c_int, _c_ptr]
+    library.hx_expert_combine.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                          _c_int, _c_int, _c_ptr]
+    library.hx_gemm_tc_grouped.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int,
+                                           _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                           _c_int, _c_ptr, _c_ptr, _c_ptr]
+    for name in ("hx_expert_tile_bound", "hx_expert_rows", "hx_expert_gather",
+                 "hx_expert_combine", "hx_gemm_tc_grouped"):
+        getattr(library, name).restype = _c_int
     library.hx_latent_prepare.argtypes = [
         _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr,
         _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
@@ -962,6 +974,72 @@ def expert_down(act: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor,
     _check(lib().hx_expert_down(act.data_ptr(), down.data_ptr(), chosen.data_ptr(),
                                 weights.data_ptr(), out.data_ptr(), out.stride(0),
                                 dtype_code(act.dtype), tokens, top, ff, width, experts, _stream()))
+
+
+GROUPED_TILES = (16, 32, 64, 128)
+
+
+def expert_tile(pairs: int, experts: int) -> int:
+    """The token tile of the grouped products: the smallest that holds an expert's average
+    share of the pairs, so that padding stays below the work."""
+    share = -(-pairs // experts)
+    for tile in GROUPED_TILES:
+        if share <= tile:
+            return tile
+    return GROUPED_TILES[-1]
+
+
+def expert_tile_bound(pairs: int, experts: int, tile: int) -> int:
+    """Tiles that ``pairs`` pairs, laid out expert by expert in whole tiles, can take."""
+    return int(lib().hx_expert_tile_bound(pairs, experts, tile))
+
+
+def expert_rows(chosen: torch.Tensor, pair_row: torch.Tensor, tile_group: torch.Tensor, pairs: int,
+                experts: int, tile: int, max_tiles: int) -> None:
+    """The pairs sorted by expert: ``pair_row[pair]`` is the pair's row in an order where every
+    expert's rows are a whole number of tiles, ``tile_group[t]`` the expert of tile ``t`` (-1
+    behind the last one in use)."""
+    _need(chosen, torch.int32, "chosen")
+    _need(pair_row, torch.int32, "pair_row")
+    _need(tile_group, torch.int32, "tile_group")
+    assert pair_row.numel() >= pairs and tile_group.numel() >= max_tiles
+    _check(lib().hx_expert_rows(chosen.data_ptr(), pairs, experts, tile, max_tiles,
+                                pair_row.data_ptr(), tile_group.data_ptr(), _stream()))
+
+
+def expert_gather(x: torch.Tensor, pair_row: torch.Tensor, grouped: torch.Tensor, tokens: int,
+                  top: int) -> None:
+    """grouped[pair_row[t * top + k]] = x[t]."""
+    assert x.dtype == grouped.dtype and x.stride(-1) == 1 and grouped.stride(-1) == 1
+    _check(lib().hx_expert_gather(x.data_ptr(), x.stride(0), pair_row.data_ptr(),
+                                  grouped.data_ptr(), grouped.stride(0), dtype_code(x.dtype),
+                                  tokens, top, x.shape[1], _stream()))
+
+
+def expert_combine(y: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tensor,
+                   out: torch.Tensor, tokens: int, top: int, width: int) -> None:
+    """out[t] += sum_k weights[t, k] * y[pair_row[t * top + k]], ``k`` ascending."""
+    _need(y, torch.float32, "y")
+    _need(out, torch.float32, "out")
+    _check(lib().hx_expert_combine(y.data_ptr(), y.stride(0), pair_row.data_ptr(),
+                                   weights.data_ptr(), out.data_ptr(), out.stride(0), tokens, top,
+                                   width, _stream()))
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, features: int,
+                    epilogue: int, up_row_offset: int, token_tile: int, tile_group: torch.Tensor,
+                    status: torch.Tensor) -> None:
+    """Tile ``t`` of ``token_tile`` rows of ``x`` times matrix ``tile_group[t]`` of ``w``
+    ``[groups, group_rows, depth]`` on the tensor cores; ``rows`` bounds the rows in use (a
+    multiple of the tile).  Epilogues: plain store, float32 store, gated activation."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    assert w.is_contiguous() and x.stride(-1) == 1 and out.stride(-1) == 1
+    groups, group_rows, depth = w.shape
+    _check(lib().hx_gemm_tc_grouped(x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), depth,
+                                    group_rows, groups, out.data_ptr(), out.stride(0), rows,
+                                    features, depth, epilogue, up_row_offset, token_tile,
+                                    tile_group.data_ptr(), status.data_ptr(), _stream()))
 
 
 # ---------------------------------------------------------- attention over a cached latent

@@ -185,8 +185,48 @@ class RoutedExperts(FeedForward):
                   (ctx.capacity * self.top, self.intermediate), ctx.dtype)
         project(x, self.w_router, sums, n, ops.EPI_STORE_F32, ctx.status)
         ops.route_top(sums, chosen, weights, n, self.experts, self.top, self.scale)
+        if self.grouped(ctx, n):
+            self.forward_grouped(ctx, x, chosen, weights, residual)
+            return
         ops.expert_gate_up(x, self.w_gate_up, chosen, act, n, self.top, self.activation)
         ops.expert_down(act, self.w_down, chosen, weights, residual, n, self.top)
+
+    # Fewer pairs than this and an expert's matrices are read about once anyway: a product
+    # per pair streams them; from here on the pairs are sorted by expert.
+    GROUPED_FROM_PAIRS = 32
+
+    def grouped(self, ctx: StepContext, tokens: int) -> bool:
+        return (ctx.dtype == torch.bfloat16 and tokens * self.top >= self.GROUPED_FROM_PAIRS
+                and self.hidden_size % 8 == 0 and self.intermediate % 8 == 0)
+
+    def forward_grouped(self, ctx: StepContext, x: torch.Tensor, chosen: torch.Tensor,
+                        weights: torch.Tensor, residual: torch.Tensor) -> None:
+        """Pairs sorted by expert, two grouped tensor-core products (the gated activation is the
+        first one's epilogue, the second stores float32 sums), and the weighted sum per token
+        in the order of its choices."""
+        n, get = ctx.n_tokens, ctx.workspace.get
+        pairs = n * self.top
+        tile = ops.expert_tile(pairs, self.experts)
+        tiles = ops.expert_tile_bound(pairs, self.experts, tile)
+        # buffers are made once for the largest step: the widest tile pads the most rows
+        most = max(ops.expert_tile_bound(ctx.capacity * self.top, self.experts, t) * t
+                   for t in ops.GROUPED_TILES)
+        pair_row = get(f"experts.pair_row/{self.top}", (ctx.capacity * self.top,), torch.int32)
+        tile_group = get(f"experts.tile_group/{self.experts}x{self.top}",
+                         (ops.expert_tile_bound(ctx.capacity * self.top, self.experts,
+                                                ops.GROUPED_TILES[0]),), torch.int32)
+        rows_in = get(f"experts.rows_in/{self.hidden_size}", (most, self.hidden_size), ctx.dtype)
+        rows_act = get(f"experts.rows_act/{self.intermediate}", (most, self.intermediate), ctx.dtype)
+        rows_out = get(f"experts.rows_out/{self.hidden_size}", (most, self.hidden_size),
+                       torch.float32)
+        ops.expert_rows(chosen, pair_row, tile_group, pairs, self.experts, tile, tiles)
+        ops.expert_gather(x, pair_row, rows_in, n, self.top)
+        epilogue = ops.EPI_GEGLU_TANH if self.activation == ops.GATE_GELU_TANH else ops.EPI_SWIGLU
+        ops.gemm_tc_grouped(rows_in, self.w_gate_up, rows_act, tiles * tile, self.intermediate,
+                            epilogue, self.intermediate, tile, tile_group, ctx.status)
+        ops.gemm_tc_grouped(rows_act, self.w_down, rows_out, tiles * tile, self.hidden_size,
+                            ops.EPI_STORE_F32, 0, tile, tile_group, ctx.status)
+        ops.expert_combine(rows_out, pair_row, weights, residual, n, self.top, self.hidden_size)
 
 
 register_part("feed_forward", "gated_mlp", GatedMlp)

@@ -167,11 +167,88 @@ int hx_outer_product_scan(const void* r, int ld_r, const void* k, int ld_k, cons
                           const int* request_start,
                           const int* request_slot, int requests, int tokens, int heads, int dim,
                           cudaStream_t stream);
+/* linear attention with a dim x vdim matrix per head.  delta == 0: S = g S + k v', o = S' q;
+ * delta != 0: S = g S, u = beta (v - S' k), S += k u', o = S' q.  g: exp(-exp(a_log) *
+ * softplus(decay_in + dt_bias)) from a projected column per head, or the constants fixed_decay
+ * (with fixed_decay_m1 = fixed_decay - 1) when decay_in is null; beta = sigmoid(beta_in).
+ * Before the recurrence q and k may be rotated by the position (positions + freq, freq_exact
+ * in the float32 engine; layout 0 interleaved, 1 halves), made unit vectors (unit_norm:
+ * x / sqrt(sum x^2 + unit_eps)) and scaled.  Head h reads q/k head h / (heads / qk_heads);
+ * o float32 [tokens][heads * vdim] */
+int hx_linear_state_scan(const void* q, int ld_q, const void* k, int ld_k, const void* v,
+                         int ld_v, int dtype, int delta, const void* decay_in,
+                         const void* beta_in, int ld_gates, const float* a_log,
+                         const float* dt_bias, const float* fixed_decay,
+                         const float* fixed_decay_m1, const int* positions, const float* freq,
+                         const double* freq_exact, int rotary_dim, int rotary_layout,
+                         int unit_norm, float unit_eps, float q_scale, float k_scale,
+                         float* state, long long state_stride, int head_stride, float* o,
+                         const int* request_start, const int* request_slot, int requests,
+                         int tokens, int heads, int qk_heads, int dim, int vdim,
+                         cudaStream_t stream);
 /* channels in `groups` equal parts, each over its root mean square, times weight; the gate
  * silu(gate) multiplies before the norm (gate_after 0) or after it (1) */
 int hx_gated_group_norm(const float* y, int ld_y, const void* gate, int ld_gate, int dtype,
                         const float* weight, void* out, int ld_out, int tokens, int channels,
                         int groups, float eps, int gate_after, cudaStream_t stream);
+
+/* ---- gated connection, joined streams --------------------------------------------------- */
+/* residual[t][c] += output[t][c] * sigmoid(gate[t][c] + bias[c]), all float32 */
+int hx_gated_residual_add(float* residual, const float* output, const float* gate, int ld_gate,
+                          const float* bias, int tokens, int width, cudaStream_t stream);
+/* out[t] = [a[t] | b[t]] in the compute dtype (a, b float32 [tokens][width]) */
+int hx_join_rows(const float* a, const float* b, void* out, int ld_out, int dtype, int tokens,
+                 int width, cudaStream_t stream);
+
+/* ---- routed experts --------------------------------------------------------------------- */
+/* s = sigmoid(sums); the `top` largest (lowest index among equals); weights s / (sum of the
+ * chosen + 1e-20) * scale; chosen and weights [tokens][top] */
+int hx_route_top(const float* sums, int ld, int tokens, int experts, int top, float scale,
+                 int* chosen, float* weights, cudaStream_t stream);
+/* act[t * top + k] = f(Wg[e] x[t]) * (Wu[e] x[t]), e = chosen[t][k]; gate_up [experts][2 ff]
+ * [width] (gate rows first) */
+int hx_expert_gate_up(const void* x, int ld_x, const void* gate_up, const int* chosen, void* act,
+                      int dtype, int tokens, int top, int ff, int width, int experts,
+                      int activation, cudaStream_t stream);
+/* out[t] += sum_k weights[t][k] * Wd[chosen[t][k]] act[t * top + k], k ascending; out float32 */
+int hx_expert_down(const void* act, const void* down, const int* chosen, const float* weights,
+                   float* out, int ld_out, int dtype, int tokens, int top, int ff, int width,
+                   int experts, cudaStream_t stream);
+
+/* The pairs (token, choice) of a step sorted by expert, every expert's rows a whole number of
+ * tiles: pair_row[pair] (-1: no valid expert), tile_group[t] the expert of tile t (-1 behind
+ * the last in use); max_tiles >= hx_expert_tile_bound(pairs, experts, tile) */
+int hx_expert_tile_bound(int pairs, int experts, int tile);
+int hx_expert_rows(const int* chosen, int pairs, int experts, int tile, int max_tiles,
+                   int* pair_row, int* tile_group, cudaStream_t stream);
+/* grouped[pair_row[t * top + k]] = x[t] */
+int hx_expert_gather(const void* x, int ld_x, const int* pair_row, void* grouped, int ld_grouped,
+                     int dtype, int tokens, int top, int width, cudaStream_t stream);
+/* out[t] += sum_k weights[t][k] * y[pair_row[t * top + k]], k ascending; y, out float32 */
+int hx_expert_combine(const float* y, int ld_y, const int* pair_row, const float* weights,
+                      float* out, int ld_out, int tokens, int top, int width,
+                      cudaStream_t stream);
+
+/* ---- attention over a cached latent ----------------------------------------------------- */
+/* down [tokens][q_rank + kv_rank + rot] float32: both latents RMS-normed with a weight; the
+ * query latent goes to query_latent; the key row [c | rot(kr) | 0..] and the value row
+ * [c | 0..] (row_dim wide each) go to `rows` at key_offset and behind it */
+int hx_latent_prepare(const float* down, int ld_down, const float* q_weight,
+                      const float* kv_weight, float eps, const int* positions, const float* freq,
+                      const double* freq_exact, int rotary_dims, int layout, void* query_latent,
+                      int ld_latent, void* rows, int ld_rows, int key_offset, int dtype,
+                      int tokens, int q_rank, int kv_rank, int rot, int row_dim,
+                      cudaStream_t stream);
+/* every head's rotated query part (q at rot_offset inside a head), turned by the position,
+ * behind the head's kv_rank latent coordinates in `rows`, zeros to row_dim */
+int hx_latent_queries(const void* q, int ld_q, int rot_offset, void* rows, int ld_rows,
+                      const int* positions, const float* freq, const double* freq_exact,
+                      int rotary_dims, int layout, int dtype, int tokens, int heads, int kv_rank,
+                      int rot, int row_dim, cudaStream_t stream);
+/* out[t][h * out_stride + o] = sum_i w[h][o][i] * x[t][h * x_stride + i] */
+int hx_head_products(const void* x, int ld_x, int x_stride, const void* w, void* out, int ld_out,
+                     int out_stride, int dtype, int tokens, int heads, int out_dim, int in_dim,
+                     cudaStream_t stream);
 
 /* ---- rotation from positions, normed heads, rotated values + cache append --------------- */
 /* heads are row_dim wide (head_dim / value_dim real coordinates); q_norm, k_norm (both or
@@ -228,6 +305,14 @@ int hx_gemm_tc_rope_append(const void* x, int ldx, int x_capacity_rows, const vo
                            const float* sin_table, int table_positions, int heads, int kv_heads,
                            int head_dim, int rotary_dim, int page_size, int num_pages, int* status,
                            cudaStream_t stream);
+
+/* grouped product: rows of x come in tiles of token_tile (16..256), tile t multiplies with
+ * group tile_group[t] of w (`groups` matrices of group_rows rows one below the other); a
+ * negative entry skips the tile; tile_group is device memory, written on the stream before */
+int hx_gemm_tc_grouped(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                       int group_rows, int groups, void* out, int ldo, int tokens, int features,
+                       int depth, int epilogue, int up_row_offset, int token_tile,
+                       const int* tile_group, int* status, cudaStream_t stream);
 
 /* ---- attention over the paged cache ----------------------------------------------------- */
 int hx_cache_chunk_elements(int dtype, int head_dim);

@@ -176,6 +176,15 @@ def retention_scan(q: np.ndarray, k: np.ndarray, v: np.ndarray, decay: np.ndarra
     return out
 
 
+def router_margins(h: np.ndarray, router: np.ndarray, top: int) -> np.ndarray:
+    """Per token, how far the router's sum of the last chosen expert lies above that of the best
+    one left out (infinite when every expert is chosen): a small margin is a close call."""
+    sums = np.sort(h @ router.T, axis=1)[:, ::-1]
+    if top >= sums.shape[1]:
+        return np.full(h.shape[0], np.inf)
+    return sums[:, top - 1] - sums[:, top]
+
+
 def routed_experts(h: np.ndarray, router: np.ndarray, experts: List[Dict[str, np.ndarray]],
                    top: int, scale: float, rnd: Callable) -> np.ndarray:
     """Sigmoid scores, the ``top`` largest, normalised to sum one, times ``scale``."""
@@ -200,6 +209,8 @@ class PlainMedolorn:
         self.eps = float(config["norm"]["eps"])
         self.width = int(config["width"])
         self.taps = int(config["canon"]["taps"])
+        # a list: every run of a feed-forward appends its tokens' router margins
+        self.margins: Optional[List[np.ndarray]] = None
 
     @classmethod
     def from_folder(cls, folder: str) -> "PlainMedolorn":
@@ -273,6 +284,8 @@ class PlainMedolorn:
         router = m["router"]
         experts = [{name: self.t[f"{p}.e{e}.{name}"] for name in ("gate", "up", "down")}
                    for e in range(int(router["experts"]))]
+        if self.margins is not None:
+            self.margins.append(router_margins(h, self.t[f"{p}.router"], int(router["top"])))
         return routed_experts(h, self.t[f"{p}.router"], experts, int(router["top"]),
                               float(router["scale"]), rnd)
 
