@@ -53,6 +53,10 @@ struct PrefillArgs {
   int* status;
   int window;       // 0: every earlier key; else the query at p sees key j <= p with p - j < window
   int keep_first;   // ... or j < keep_first (used with a window only)
+  int pack;         // 1: a CTA's rows are 64 tokens of one head.  G > 1 (the heads per key/value
+                    // head, at most 64): its rows are the G heads of 64 / G tokens, token by
+                    // token, so the heads that share keys and values read them once; the
+                    // grid's second dimension then counts key/value heads
 };
 
 constexpr int RING = 2;                         // key/value tiles in flight per CTA
@@ -105,20 +109,23 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int head = blockIdx.y;
-  const int kv_head = head / (a.heads / a.kv_heads);
+  const int pack = a.pack;
+  const int kv_head = pack > 1 ? blockIdx.y : blockIdx.y / (a.heads / a.kv_heads);
+  const int head0 = pack > 1 ? kv_head * pack : blockIdx.y;   // head of a token's first row
+  const int tile_tokens = BLOCK_M / pack;                     // tokens a tile of rows holds
 
   // which request and which 64-row tile of it is this CTA?
   int tile_in_request = 0, tiles_of_request = 0;
-  const int request = hx_find_query_tile(a.request_start, a.requests, a.min_query_len, BLOCK_M,
+  const int request = hx_find_query_tile(a.request_start, a.requests, a.min_query_len, tile_tokens,
                                          blockIdx.x, tile_in_request, tiles_of_request);
   if (request < 0) return;
   const int q_begin = a.request_start[request];
   const int q_len = a.request_start[request + 1] - q_begin;
   const int context = a.request_context[request];
-  const int row0 = tile_in_request * BLOCK_M;                 // first query row of the tile
-  const int rows_here = min(BLOCK_M, q_len - row0);
-  const int last_key = context + row0 + rows_here - 1;        // last key any row here sees
+  const int row0 = tile_in_request * tile_tokens;             // first token of the tile
+  const int tokens_here = min(tile_tokens, q_len - row0);
+  const int rows_here = tokens_here * pack;
+  const int last_key = context + row0 + tokens_here - 1;      // last key any row here sees
   // With a window the CTA walks the tiles that hold kept first keys, then the tiles from the
   // one that holds the first key its FIRST row sees through the window; `n_tiles` counts
   // both runs and tile_at(i) is the i-th of them.  Keys from keep_first up to first_needed
@@ -192,11 +199,12 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
   const int warp_row = warp * 16;
   uint32_t q_frag[kDSteps][4];
   {
-    const int r0 = warp_row + (lane >> 2), r1 = r0 + 8;
-    const __nv_bfloat16* q0 = a.q + static_cast<size_t>(q_begin + row0 + min(r0, rows_here - 1)) * a.ldq +
-                              static_cast<size_t>(head) * D + 2 * (lane & 3);
-    const __nv_bfloat16* q1 = a.q + static_cast<size_t>(q_begin + row0 + min(r1, rows_here - 1)) * a.ldq +
-                              static_cast<size_t>(head) * D + 2 * (lane & 3);
+    const int r0 = min(warp_row + (lane >> 2), rows_here - 1);
+    const int r1 = min(warp_row + (lane >> 2) + 8, rows_here - 1);
+    const __nv_bfloat16* q0 = a.q + static_cast<size_t>(q_begin + row0 + r0 / pack) * a.ldq +
+                              static_cast<size_t>(head0 + r0 % pack) * D + 2 * (lane & 3);
+    const __nv_bfloat16* q1 = a.q + static_cast<size_t>(q_begin + row0 + r1 / pack) * a.ldq +
+                              static_cast<size_t>(head0 + r1 % pack) * D + 2 * (lane & 3);
 #pragma unroll
     for (int k = 0; k < kDSteps; ++k) {
       q_frag[k][0] = *reinterpret_cast<const uint32_t*>(q0 + k * 16);
@@ -227,8 +235,10 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
     for (int e = 0; e < 4; ++e) o_acc[n][e] = 0.0f;
   float row_max[2] = {-INFINITY, -INFINITY};
   float row_sum[2] = {0.0f, 0.0f};
-  const int q_pos0 = context + row0 + warp_row + (lane >> 2);   // position of the first row
-  const int q_pos1 = q_pos0 + 8;
+  const int q_pos0 = context + row0 + (warp_row + (lane >> 2)) / pack;   // position of the first row
+  const int q_pos1 = context + row0 + (warp_row + (lane >> 2) + 8) / pack;
+  const int warp_pos_first = context + row0 + warp_row / pack;           // of the warp's 16 rows
+  const int warp_pos_last = context + row0 + (warp_row + 15) / pack;
 
   for (int turn = 0; turn < n_tiles; ++turn) {
     const int tile = tile_at(turn);
@@ -286,9 +296,8 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
     const int key0 = tile * BLOCK_N + 2 * (lane & 3);
     // a tile needs the mask when it reaches beyond the first row's own key, or (window) when
     // its first key lies outside the window of this warp's last row
-    const bool needs_mask = tile * BLOCK_N + BLOCK_N - 1 > context + row0 + warp_row ||
-                            (a.window > 0 &&
-                             context + row0 + warp_row + 15 - tile * BLOCK_N >= a.window);
+    const bool needs_mask = tile * BLOCK_N + BLOCK_N - 1 > warp_pos_first ||
+                            (a.window > 0 && warp_pos_last - tile * BLOCK_N >= a.window);
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < BLOCK_N / 8; ++n) {
@@ -374,8 +383,8 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
   for (int r = 0; r < 2; ++r) {
     const int row = warp_row + (lane >> 2) + r * 8;
     if (row >= rows_here) continue;
-    __nv_bfloat16* dst = a.out + static_cast<size_t>(q_begin + row0 + row) * a.ldo +
-                         static_cast<size_t>(head) * D + 2 * (lane & 3);
+    __nv_bfloat16* dst = a.out + static_cast<size_t>(q_begin + row0 + row / pack) * a.ldo +
+                         static_cast<size_t>(head0 + row % pack) * D + 2 * (lane & 3);
 #pragma unroll
     for (int n = 0; n < kOBlocks; ++n) {
       const __nv_bfloat162 value = __floats2bfloat162_rn(o_acc[n][r * 2] * inverse[r],
@@ -398,7 +407,7 @@ int launch(const PrefillArgs& a, int tiles, cudaStream_t stream) {
     }
     configured = true;
   }
-  const dim3 grid(tiles, a.heads);
+  const dim3 grid(tiles, a.pack > 1 ? a.kv_heads : a.heads);
   hx_launch(prefill_attention_kernel<D>, grid, THREADS, kSmem, stream, a);
   return HX_OK;
 }
@@ -415,14 +424,15 @@ HX_API int hx_prefill_attention_supports(int head_dim, int page_size) {
 // `tile_bound` is an upper bound of the number of 64-row query tiles over those requests
 // (tokens / 64 + requests is always enough).
 // window > 0: the query at position p sees key j <= p when p - j < window or j < keep_first.
-HX_API int hx_prefill_attention_windowed(const void* q, int ldq, const void* k_cache,
+namespace {
+int prefill_attention(const void* q, int ldq, const void* k_cache,
                                          const void* v_cache, const int* request_start,
                                          const int* request_context, const int* request_table_row,
                                          const int* block_tables, int table_stride, void* out,
                                          int ldo, int requests, int tile_bound, int heads,
                                          int kv_heads, int head_dim, int page_size, int num_pages,
                                          float scale, int min_query_len, int window,
-                                         int keep_first, int* status, cudaStream_t stream) {
+                                         int keep_first, int pack, int* status, cudaStream_t stream) {
   HX_REQUIRE(window >= 0 && keep_first >= 0, "hx_prefill_attention: bad window");
   if (window == 0) keep_first = 0;
   HX_REQUIRE(hx_prefill_attention_supports(head_dim, page_size),
@@ -444,7 +454,7 @@ HX_API int hx_prefill_attention_windowed(const void* q, int ldq, const void* k_c
                 static_cast<const __nv_bfloat16*>(v_cache), request_start, request_context,
                 request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(out),
                 ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status,
-                window, keep_first};
+                window, keep_first, pack};
   int rc = HX_ERR_UNSUPPORTED;
   switch (head_dim) {
     case 16: rc = launch<16>(a, tile_bound, stream); break;
@@ -463,6 +473,51 @@ HX_API int hx_prefill_attention_windowed(const void* q, int ldq, const void* k_c
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_prefill_attention");
   return HX_OK;
+}
+}  // namespace
+
+HX_API int hx_prefill_attention_windowed(const void* q, int ldq, const void* k_cache,
+                                         const void* v_cache, const int* request_start,
+                                         const int* request_context, const int* request_table_row,
+                                         const int* block_tables, int table_stride, void* out,
+                                         int ldo, int requests, int tile_bound, int heads,
+                                         int kv_heads, int head_dim, int page_size, int num_pages,
+                                         float scale, int min_query_len, int window,
+                                         int keep_first, int* status, cudaStream_t stream) {
+  return prefill_attention(q, ldq, k_cache, v_cache, request_start, request_context,
+                           request_table_row, block_tables, table_stride, out, ldo, requests,
+                           tile_bound, heads, kv_heads, head_dim, page_size, num_pages, scale,
+                           min_query_len, window, keep_first, 1, status, stream);
+}
+
+// Query tiles of hx_prefill_attention_packed hold this many tokens (0: the heads per key/value
+// head are more than a tile's rows, or one, and the kernel does not apply).
+HX_API int hx_prefill_attention_packed_tokens(int heads, int kv_heads) {
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0) return 0;
+  const int group = heads / kv_heads;
+  return group > 1 && group <= BLOCK_M ? BLOCK_M / group : 0;
+}
+
+// The same attention with the heads that share a key/value head side by side in a CTA's rows:
+// keys and values are read once for all of them, which is what decides the time when many
+// heads share one cached row (one token's heads fill half a tile's rows already).  Takes
+// requests of any length from `min_query_len` on, single decoded tokens too; `tile_bound`
+// counts tiles of hx_prefill_attention_packed_tokens(heads, kv_heads) tokens.
+HX_API int hx_prefill_attention_packed(const void* q, int ldq, const void* k_cache,
+                                       const void* v_cache, const int* request_start,
+                                       const int* request_context, const int* request_table_row,
+                                       const int* block_tables, int table_stride, void* out,
+                                       int ldo, int requests, int tile_bound, int heads,
+                                       int kv_heads, int head_dim, int page_size, int num_pages,
+                                       float scale, int min_query_len, int window,
+                                       int keep_first, int* status, cudaStream_t stream) {
+  HX_REQUIRE(hx_prefill_attention_packed_tokens(heads, kv_heads) > 0,
+             "hx_prefill_attention_packed: %d heads on %d key/value heads do not pack", heads,
+             kv_heads);
+  return prefill_attention(q, ldq, k_cache, v_cache, request_start, request_context,
+                           request_table_row, block_tables, table_stride, out, ldo, requests,
+                           tile_bound, heads, kv_heads, head_dim, page_size, num_pages, scale,
+                           min_query_len, window, keep_first, heads / kv_heads, status, stream);
 }
 
 HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,

@@ -106,6 +106,10 @@ def _declare(library: ctypes.CDLL) -> None:
         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
         _c_ptr, _c_ptr]
     library.hx_prefill_attention_windowed.restype = _c_int
+    library.hx_prefill_attention_packed.argtypes = library.hx_prefill_attention_windowed.argtypes
+    library.hx_prefill_attention_packed.restype = _c_int
+    library.hx_prefill_attention_packed_tokens.argtypes = [_c_int, _c_int]
+    library.hx_prefill_attention_packed_tokens.restype = _c_int
     library.hx_prefill_attention_tc_windowed.argtypes = \
         library.hx_prefill_attention_windowed.argtypes
     library.hx_prefill_attention_tc_windowed.restype = _c_int
@@ -575,6 +579,11 @@ def prefill_attention_tc_supports(head_dim: int, page_size: int) -> bool:
     return bool(lib().hx_prefill_attention_tc_supports(head_dim, page_size))
 
 
+def prefill_attention_packed_tokens(heads: int, kv_heads: int) -> int:
+    """Tokens a query tile of the packed kernel holds; 0 where it does not apply."""
+    return int(lib().hx_prefill_attention_packed_tokens(heads, kv_heads))
+
+
 def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       request_start: torch.Tensor, request_context: torch.Tensor,
                       request_table_row: torch.Tensor, block_tables: torch.Tensor,
@@ -583,7 +592,7 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       min_query_len: int, status: torch.Tensor,
                       tensor_memory: Optional[bool] = None,
                       query_lengths: Optional[Sequence[int]] = None, window: int = 0,
-                      keep_first: int = 0) -> None:
+                      keep_first: int = 0, packed: bool = False) -> None:
     """Tensor-core attention (bfloat16) of every request that brings at least
     ``min_query_len`` tokens; ``tile_bound`` bounds the number of query tiles of 64 tokens
     (the tensor-memory kernel, whose tiles hold 256 tokens, needs no more).  A CTA that finds
@@ -593,14 +602,21 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     ``tensor_memory``: take the tcgen05 kernel (scores, probabilities and output in tensor
     memory; pages of at least 16 keys) or the ``mma.sync`` kernel; default: tcgen05 where it
     applies.  ``window`` > 0: the query at position p sees key j <= p when p - j < window or
-    j < ``keep_first``; both kernels skip the tiles of keys that no row of a query tile sees."""
+    j < ``keep_first``; both kernels skip the tiles of keys that no row of a query tile sees.
+    ``packed``: the ``mma.sync`` kernel with the heads of a key/value head side by side in a
+    tile's rows (``prefill_attention_packed_tokens`` tokens a tile), which reads keys and
+    values once for all of them; it takes single decoded tokens as well."""
     _need(q, torch.bfloat16, "q")
     _need(k_cache, torch.bfloat16, "k_cache")
     _need(out, torch.bfloat16, "out")
-    if tensor_memory is None:
+    if packed:
+        tensor_memory = False
+    elif tensor_memory is None:
         tensor_memory = prefill_attention_tc_supports(head_dim, page_size)
     if query_lengths is not None:
         rows = PREFILL_TILE_ROWS_TC if tensor_memory else PREFILL_TILE_ROWS
+        if packed:
+            rows = prefill_attention_packed_tokens(heads, kv_heads)
         tile_bound = sum(-(-length // rows) for length in query_lengths
                          if length >= min_query_len)
         if tile_bound == 0:
@@ -610,7 +626,10 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         request_context.data_ptr(), request_table_row.data_ptr(), block_tables.data_ptr(),
         block_tables.stride(0), out.data_ptr(), out.stride(0), requests, tile_bound, heads,
         kv_heads, head_dim, page_size, num_pages, float(scale), min_query_len)
-    if tensor_memory:
+    if packed:
+        _check(lib().hx_prefill_attention_packed(*arguments, int(window), int(keep_first),
+                                                 _ptr(status), _stream()))
+    elif tensor_memory:
         _check(lib().hx_prefill_attention_tc_windowed(*arguments, int(window), int(keep_first),
                                                       _ptr(status), _stream()))
     else:

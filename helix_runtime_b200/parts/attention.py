@@ -82,6 +82,8 @@ def rotary_row_permutation(heads: int, head_dim: int, rotary_dim: int) -> torch.
 
 
 class PagedAttention(Mixer):
+    pack_heads = False      # subclasses whose heads share few cached rows set this
+
     def __init__(self, spec: PartSpec, hidden_size: int) -> None:
         super().__init__(spec, hidden_size)
         self.heads = int(spec["num_heads"])
@@ -279,6 +281,18 @@ class PagedAttention(Mixer):
         tensor_cores = (ctx.dtype == torch.bfloat16
                         and ctx.max_query_len >= TENSOR_CORE_MIN_QUERY
                         and ops.prefill_attention_supports(self.row_dim, cache.page_size))
+        # many heads on one cached row: the kernel whose rows are a token's heads reads the
+        # row once for all of them, decoded tokens included
+        if (self.pack_heads and ctx.dtype == torch.bfloat16
+                and ops.prefill_attention_supports(self.row_dim, cache.page_size)
+                and ops.prefill_attention_packed_tokens(self.heads, self.kv_heads) > 0):
+            ops.prefill_attention(qkv, cache.keys, cache.values, ctx.request_start,
+                                  ctx.request_context, ctx.request_slot, cache.block_tables,
+                                  context, ctx.n_requests, n, self.heads, self.kv_heads,
+                                  self.row_dim, cache.page_size, cache.num_pages, self.scale, 1,
+                                  ctx.status, query_lengths=ctx.host_query_lengths,
+                                  window=window, keep_first=kept, packed=True)
+            return
         if tensor_cores:
             ops.prefill_attention(qkv, cache.keys, cache.values, ctx.request_start,
                                   ctx.request_context, ctx.request_slot, cache.block_tables,
@@ -372,6 +386,8 @@ class LatentAttention(PagedAttention):
     value up-projection ``Uv_h`` follows it.  The attention kernels are those of
     :class:`PagedAttention`, with one key/value head and rows of ``row_dim``.
     """
+
+    pack_heads = True       # every head attends to the one cached row
 
     def __init__(self, spec: PartSpec, hidden_size: int) -> None:
         Mixer.__init__(self, spec, hidden_size)

@@ -365,6 +365,18 @@ int hx_prefill_attention_windowed(const void* q, int ldq, const void* k_cache, c
                                   int page_size, int num_pages, float scale, int min_query_len,
                                   int window, int keep_first, int* status, cudaStream_t stream);
 
+/* the same with the heads of a key/value head side by side in a tile's rows (2 to 64 heads
+ * per key/value head): keys and values are read once for all of them; requests of any length
+ * from min_query_len on; tile_bound counts tiles of hx_prefill_attention_packed_tokens tokens */
+int hx_prefill_attention_packed_tokens(int heads, int kv_heads);
+int hx_prefill_attention_packed(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                const int* request_start, const int* request_context,
+                                const int* request_table_row, const int* block_tables,
+                                int table_stride, void* out, int ldo, int requests,
+                                int tile_bound, int heads, int kv_heads, int head_dim,
+                                int page_size, int num_pages, float scale, int min_query_len,
+                                int window, int keep_first, int* status, cudaStream_t stream);
+
 /* the same on tcgen05, scores and partial outputs in tensor memory (pages of 16, 32, 64) */
 int hx_prefill_attention_tc_supports(int head_dim, int page_size);
 int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache, const void* v_cache,

@@ -437,3 +437,37 @@ def test_one_small_product_per_head(tokens, heads, out_dim, in_dim, dtype):
     close(got[:, :, :out_dim], want, 3e-6 if dtype == torch.float32 else 2e-2,
           1e-6 if dtype == torch.float32 else 8e-3)
     assert (got[:, :, out_dim:] == 9.0).all()
+
+
+# ------------------------------ attention with a token's heads side by side in a tile's rows
+
+@pytest.mark.parametrize("heads,kv_heads", [(6, 1), (32, 1), (8, 2), (3, 1), (64, 1), (10, 5)])
+@pytest.mark.parametrize("window,keep", [(0, 0), (1, 0), (19, 0), (64, 0), (70, 6)])
+def test_heads_that_share_a_cached_row_side_by_side(heads, kv_heads, window, keep):
+    """Prompt portions and single decoded tokens, with and without a window, pages that the
+    window has given back taken out of the table; group sizes that divide a tile's 64 rows and
+    that do not."""
+    from test_rekasun_kernels_gpu import assert_close as close_rows, tolerance, windowed_case
+    rng = np.random.default_rng(heads)
+    for context, new in [(0, 150), (37, 90), (210, 17), (129, 1), (15, 1), (0, 1), (100, 23)]:
+        head_dim, page = ((48, 16) if heads % 2 else (32, 8))
+        out, expected, _ = windowed_case(rng, torch.bfloat16, heads, kv_heads, head_dim, page,
+                                         context, new, window, keep, tensor_cores="packed",
+                                         free_dead_pages=window > 0)
+        close_rows(out, expected, f"{heads} heads, window {window} keep {keep}, context "
+                   f"{context}, {new} new", **tolerance(torch.bfloat16, 2e-5))
+
+
+def test_a_key_at_the_windows_edge_for_every_head_of_a_token():
+    from test_rekasun_kernels_gpu import edge_keys, windowed_case
+    rng = np.random.default_rng(32)
+    window, keep = 48, 0
+    for new in (1, 80):
+        for key, _ in edge_keys(299, window, keep):
+            seen = 299 - key < window
+            out, expected, values = windowed_case(rng, torch.bfloat16, 6, 1, 32, 16, 300 - new, new,
+                                                  window, keep, dominant=(new - 1, key),
+                                                  tensor_cores="packed")
+            wanted = np.repeat(values[:, key], 6, axis=0).reshape(-1)
+            distance = float(np.abs(out[-1] - wanted).max())
+            assert (distance < 3e-2) == seen, f"key {key} seen={seen}: distance {distance}"

@@ -253,9 +253,10 @@ def windowed_case(rng, dtype, heads, kv_heads, head_dim, page_size, context, new
     starts, slots = dev([0, new], torch.int32), dev([1], torch.int32)
     if tensor_cores:
         ops.prefill_attention(*common, starts, dev([context], torch.int32), slots,
-                              dev(tables, torch.int32), out, 1, new // 64 + 1, heads, kv_heads,
+                              dev(tables, torch.int32), out, 1, new, heads, kv_heads,
                               head_dim, page_size, num_pages, scale, 1, status, window=window,
-                              keep_first=keep, tensor_memory=tensor_memory)
+                              keep_first=keep, tensor_memory=tensor_memory,
+                              packed=tensor_cores == "packed")
     else:
         longest = min(total, window + keep)
         max_splits = max(1, -(-longest // split_keys))
