@@ -365,6 +365,10 @@ struct PersistentArgs {
   int whole_rounds;           // >= 0: the tiles behind this many whole rounds are shared out by
                               // k-blocks (add epilogue only); -1: every unit is a whole tile
   int activation;             // gated epilogue: what the gate passes through (HxGateActivation)
+  // Grouped product (see GemmArgs): token tile t multiplies with group tile_group[t] of the
+  // weight matrix; a unit of a tile with a negative group loads, multiplies and writes nothing.
+  const int* tile_group;
+  int group_rows;
 };
 
 // What a CTA works on at a time: a tile, or (`partial`) a run of k-blocks of a tile that
@@ -664,10 +668,16 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
       uint32_t fill = 0;      // stages filled so far, over all units
       Unit unit;
       for (int iteration = 0; unit_at(args, iteration, unit) && !*failed; ++iteration) {
-        const int feature0 = unit.feature_tile * FEATURES;
+        int group_row0 = 0, kb_end = unit.kb_end;
+        if (args.tile_group != nullptr) {
+          const int group = args.tile_group[unit.token_tile];
+          if (group < 0) kb_end = unit.kb_begin;
+          else group_row0 = group * args.group_rows;
+        }
+        const int feature0 = group_row0 + unit.feature_tile * FEATURES;
         const int second_half = EPI == EPI_SWIGLU ? args.up_row_offset + feature0 : feature0 + BM;
         const int token0 = unit.token_tile * BM;
-        for (int kb = unit.kb_begin; kb < unit.kb_end; ++kb, ++fill) {
+        for (int kb = unit.kb_begin; kb < kb_end; ++kb, ++fill) {
           const int s = fill % STAGES;
           const uint32_t round = fill / STAGES;
           if (!mbar_wait(&empty_bar[s], (round & 1u) ^ 1u)) {
@@ -703,7 +713,8 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
         }
         tc_fence_after();
         const uint32_t accumulator = tmem_base + buffer * Config::kBufferColumns;
-        for (int kb = unit.kb_begin; kb < unit.kb_end; ++kb, ++drained) {
+        const bool skipped = args.tile_group != nullptr && args.tile_group[unit.token_tile] < 0;
+        for (int kb = unit.kb_begin; kb < (skipped ? unit.kb_begin : unit.kb_end); ++kb, ++drained) {
           const int s = drained % STAGES;
           const uint32_t round = drained / STAGES;
           if (!mbar_wait(&full_bar[s], round & 1u)) {
@@ -772,7 +783,7 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
                            lane_base + buffer * Config::kBufferColumns,
                            unit.token_tile * BM + quarter * 32 + lane, args.tokens,
                            unit.feature_tile * FEATURES);
-      } else {
+      } else if (args.tile_group == nullptr || args.tile_group[unit.token_tile] >= 0) {
         write_row<EPI>(args.out, args.ldo, args.features,
                        lane_base + buffer * Config::kBufferColumns,
                        unit.token_tile * BM + quarter * 32 + lane, args.tokens,
@@ -1121,6 +1132,16 @@ HX_API int hx_gemm_tc_grouped(const void* x, int ldx, int x_capacity_rows, const
   rc = get_tensor_map(x, x_capacity_rows, depth, ldx, token_tile, &map_x);
   if (rc != HX_OK) return rc;
   const int total_k_blocks = (depth + BK - 1) / BK;
+  if (token_tile == BM) {
+    // tiles of 128 tokens: the persistent kernel, as for prompt portions of a plain product
+    PersistentArgs persistent{out, ldo, tokens, features, depth, up_row_offset, 0, 0, 0,
+                              total_k_blocks, status, RopeArgs{}, -1, activation, tile_group,
+                              group_rows};
+    rc = launch_persistent_epilogue(epilogue, map_w, map_x, persistent, stream);
+    if (rc != HX_OK) return rc;
+    HX_CHECK_LAUNCH("hx_gemm_tc_grouped");
+    return HX_OK;
+  }
   GemmArgs args{out, ldo, tokens, features, depth, up_row_offset, total_k_blocks, 0, status,
                 activation, tile_group, group_rows};
   const dim3 grid((tokens + token_tile - 1) / token_tile, (features + BM - 1) / BM, 1);

@@ -995,19 +995,17 @@ def expert_down(act: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor,
                                 dtype_code(act.dtype), tokens, top, ff, width, experts, _stream()))
 
 
-GROUPED_TILES = (16, 32, 64, 128, 256)
+GROUPED_TILES = (16, 32, 64, 128)
 
 
 def expert_tile(pairs: int, experts: int) -> int:
     """The token tile of the grouped products: the smallest that holds an expert's average
     share of the pairs, so that padding stays below the work."""
     share = -(-pairs // experts)
-    for tile in GROUPED_TILES[:-1]:
+    for tile in GROUPED_TILES:
         if share <= tile:
             return tile
-    # the widest tile halves the reads of an expert's matrices but pads up to 255 rows an
-    # expert: it pays from three tiles' worth of rows on
-    return GROUPED_TILES[-1] if share >= 3 * GROUPED_TILES[-2] else GROUPED_TILES[-2]
+    return GROUPED_TILES[-1]
 
 
 def expert_tile_bound(pairs: int, experts: int, tile: int) -> int:
