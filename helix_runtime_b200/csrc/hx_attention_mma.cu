@@ -275,6 +275,9 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
       __syncthreads();
     }
 
+    // a warp none of whose 16 rows is a query (a short portion; a decoded token whose heads
+    // fill a part of the tile) leaves the tensor cores to the others
+    if (warp_row < rows_here) {
     // ---- S = Q K^T for 16 rows x 64 keys: 8 n-blocks of 8 keys
     float s[BLOCK_N / 8][4];
 #pragma unroll
@@ -364,6 +367,7 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
         hx_mma_bf16(o_acc[nn * 2 + 1], p_hi, b[2], b[3]);
         hx_mma_bf16(o_acc[nn * 2 + 1], p_lo, b[2], b[3]);
       }
+    }
     }
     __syncthreads();      // every warp is done with this stage before it is refilled
     if (tid == 0 && turn + RING < n_tiles) {
