@@ -48,7 +48,8 @@
 namespace {
 
 constexpr int WARPS_PER_BLOCK = 4;
-constexpr int MAX_HEAD_DIM = 256;
+constexpr int MAX_HEAD_DIM = 256;              // of the streaming kernel
+constexpr int MAX_CUDA_CORE_HEAD_DIM = 1024;   // of the CUDA-core kernel (a cached latent's row)
 
 struct AttentionArgs {
   const void* q;
@@ -226,7 +227,7 @@ __device__ __forceinline__ void finish_item(const AttentionArgs& a, const Item& 
 // are read two at a time, which every chunk size and every even head size allows.
 template <typename T, int DPL>
 __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(AttentionArgs a) {
-  __shared__ float q_shared[WARPS_PER_BLOCK][MAX_HEAD_DIM];
+  __shared__ float q_shared[WARPS_PER_BLOCK][MAX_CUDA_CORE_HEAD_DIM];
   hx_pdl_prologue();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -1007,20 +1008,24 @@ template <typename T>
 int launch_cuda_cores(const AttentionArgs& a, cudaStream_t stream) {
   const long long items = static_cast<long long>(a.tokens) * a.heads * a.max_splits;
   const int blocks = static_cast<int>((items + WARPS_PER_BLOCK - 1) / WARPS_PER_BLOCK);
-  if (a.head_dim % 2 != 0 || a.head_dim > MAX_HEAD_DIM) {
+  if (a.head_dim % 2 != 0 || a.head_dim > MAX_CUDA_CORE_HEAD_DIM) {
     hx_set_error("hx_paged_attention: head_dim %d is not supported (even, at most %d)",
-                 a.head_dim, MAX_HEAD_DIM);
+                 a.head_dim, MAX_CUDA_CORE_HEAD_DIM);
     return HX_ERR_UNSUPPORTED;
   }
   if (a.head_dim <= 64) {
     hx_launch(paged_attention_kernel<T, 2>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
   } else if (a.head_dim <= 128 && a.head_dim % 4 == 0) {
     hx_launch(paged_attention_kernel<T, 4>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
-  } else if (a.head_dim % 8 == 0) {
+  } else if (a.head_dim <= 256 && a.head_dim % 8 == 0) {
     hx_launch(paged_attention_kernel<T, 8>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
+  } else if (a.head_dim <= 512 && a.head_dim % 16 == 0) {
+    hx_launch(paged_attention_kernel<T, 16>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
+  } else if (a.head_dim % 32 == 0) {
+    hx_launch(paged_attention_kernel<T, 32>, blocks, WARPS_PER_BLOCK * 32, 0, stream, a);
   } else {
     hx_set_error("hx_paged_attention: head_dim %d is not supported (above 64 a multiple of 4, "
-                 "above 128 a multiple of 8)", a.head_dim);
+                 "above 128 of 8, above 256 of 16, above 512 of 32)", a.head_dim);
     return HX_ERR_UNSUPPORTED;
   }
   return HX_OK;

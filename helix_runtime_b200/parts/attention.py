@@ -63,10 +63,11 @@ TENSOR_CORE_MIN_QUERY = 16
 
 def row_width(head_dim: int) -> int:
     """The head size the tensor-core attention kernels are built for that holds ``head_dim``:
-    steps of 16 up to 128, of 32 up to 256; beyond that the head keeps its size."""
+    steps of 16 up to 128, of 32 up to 256; beyond that a head that fits the CUDA-core kernel is
+    rounded up to a step of 32 (up to 1,024) and a larger one keeps its size."""
     step = 16 if head_dim <= 128 else 32
     wide = -(-head_dim // step) * step
-    return wide if wide <= 256 else head_dim
+    return wide if wide <= 1024 else head_dim
 
 
 def rotary_row_permutation(heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
