@@ -55,7 +55,8 @@ def test_benchmark_shapes_are_valid_configurations():
 def test_heads_are_held_in_rows_the_tensor_core_kernels_tile():
     from helix_runtime_b200.parts.attention import row_width
 
-    # steps of 16 up to 128, of 32 up to 256, as it is beyond that
+    # steps of 16 up to 128, of 32 up to 1,024 (the tensor-core kernels end at 256, the
+    # CUDA-core kernel at 1,024), as it is beyond that
     assert [row_width(d) for d in (2, 16, 24, 100, 112, 128)] == [16, 16, 32, 112, 112, 128]
-    assert [row_width(d) for d in (130, 144, 160, 250, 256, 258, 512)] == \
-        [160, 160, 160, 256, 256, 258, 512]
+    assert [row_width(d) for d in (130, 144, 160, 250, 256, 258, 512, 1000, 1026)] == \
+        [160, 160, 160, 256, 256, 288, 512, 1024, 1026]
