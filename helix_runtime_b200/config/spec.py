@@ -67,13 +67,16 @@ class ScheduleEntry:
     once more; models that run a stretch of layers several times feed the input back in at
     the start of every repeat.  ``before``: a part of the family ``entry`` that is run before
     the entry's block on the residual stream and the embedding's output (a model that feeds its
-    input back in through a matrix at the start of every repeat names it here).
+    input back in through a matrix at the start of every repeat names it here).  ``after``: a
+    part of the same family that is run behind the entry's block (a model that gives every layer
+    an input of its own, looked up by the token's id, names it here).
     """
 
     block: int
     cache_from: Optional[int] = None
     add_embedding: bool = False
     before: Optional[PartSpec] = None
+    after: Optional[PartSpec] = None
 
 
 @dataclasses.dataclass(frozen=True)

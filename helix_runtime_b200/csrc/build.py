@@ -28,6 +28,7 @@ SOURCES = (
     "hx_recurrent.cu",
     "hx_rotary_norm.cu",
     "hx_gated_connection.cu",
+    "hx_normed_residual.cu",
     "hx_routed_experts.cu",
     "hx_latent.cu",
     "hx_gemm_simt.cu",

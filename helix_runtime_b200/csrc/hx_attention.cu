@@ -80,7 +80,23 @@ struct AttentionArgs {
   int split_keys;
   int max_splits;
   int* status;
+  // Optional, per query head (null: absent).  sinks: the softmax's denominator also holds
+  // exp(sinks[h]), a term without key or value.  slopes: the score of key j for the query at
+  // position i is lowered by slopes[h] * (i - j).
+  const float* sinks = nullptr;
+  const float* slopes = nullptr;
 };
+
+// A finished row with maximum m, weight l and unnormalised sum o, and a sink s: the result is
+// o * factor with factor = e^(m - M) / (l e^(m - M) + e^(s - M)), M = max(m, s).
+__device__ __forceinline__ float sink_inverse(const AttentionArgs& a, int head, float row_max,
+                                              float row_sum) {
+  if (a.sinks == nullptr) return 1.0f / row_sum;
+  const float sink = a.sinks[head];
+  const float top = fmaxf(row_max, sink);
+  const float keep = row_max == -INFINITY ? 0.0f : expf(row_max - top);
+  return keep / (row_sum * keep + expf(sink - top));
+}
 
 __device__ __forceinline__ bool skipped(const AttentionArgs& a, int token) {
   if (a.skip_query_len <= 0) return false;
@@ -162,7 +178,7 @@ __device__ void merge_splits(const AttentionArgs& a, const Item& item, int lane)
     const int here = min(32, n_splits - base);
     for (int j = 0; j < here; ++j) total_sum += __shfl_sync(0xffffffffu, weighted, j);
   }
-  const float inverse = 1.0f / total_sum;
+  const float inverse = sink_inverse(a, item.head, total_max, total_sum);
   T* out = static_cast<T*>(a.out) + static_cast<size_t>(item.token) * a.ldo +
            static_cast<size_t>(item.head) * D;
   for (int d = lane; d < D; d += 32) {
@@ -193,7 +209,7 @@ __device__ __forceinline__ void finish_item(const AttentionArgs& a, const Item& 
                                             float running_max, float running_sum) {
   const int D = a.head_dim;
   if (item.n_splits == 1) {
-    const float inverse = 1.0f / running_sum;
+    const float inverse = sink_inverse(a, item.head, running_max, running_sum);
     T* out = static_cast<T*>(a.out) + static_cast<size_t>(item.token) * a.ldo +
              static_cast<size_t>(item.head) * D + first_dim;
 #pragma unroll
@@ -279,6 +295,8 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
         dot = fmaf(qs[d + 1], hx_to_float<T>(k[1]), dot);
       }
       score = dot * a.scale;
+      if (a.slopes != nullptr)
+        score -= a.slopes[item.head] * static_cast<float>(a.positions[item.token] - key);
     }
     float chunk_max = score;
 #pragma unroll
@@ -506,7 +524,7 @@ __device__ void merge_parts(const AttentionArgs& a, int token, int head, long lo
       }
     }
   }
-  const float inverse = 1.0f / total_sum;
+  const float inverse = sink_inverse(a, head, total_max, total_sum);
   T* out = static_cast<T*>(a.out) + static_cast<size_t>(token) * a.ldo +
            static_cast<size_t>(head) * D;
 #pragma unroll
@@ -819,6 +837,14 @@ void paged_attention_stream_kernel(
       score[2 * tile + 1] = s[tile][2];
     }
     float chunk_max = -INFINITY;
+    if (a.slopes != nullptr) {
+      // the distance from the row's own position (at.keys - 1) to key group + 8 j of the chunk
+      const float slope = a.slopes[at.head] / a.scale;
+      const int distance0 = at.keys - 1 - block_key0 - group;
+#pragma unroll
+      for (int j = 0; j < 2 * kTiles; ++j)
+        score[j] -= slope * static_cast<float>(distance0 - 8 * j);
+    }
     if (keys_here == KEYS && bad_pages == 0u && window_from <= 0) {
 #pragma unroll
       for (int j = 0; j < 2 * kTiles; ++j) {
@@ -900,7 +926,7 @@ void paged_attention_stream_kernel(
       const long long row_end = at.row_begin + at.n;
       if (at.row_begin >= my_begin && row_end <= my_end) {
         if (quad == 0) {
-          const float inverse = 1.0f / row_sum;
+          const float inverse = sink_inverse(a, at.head, running_max, row_sum);
           T* out = static_cast<T*>(a.out) + static_cast<size_t>(at.token) * a.ldo +
                    static_cast<size_t>(at.head) * D + group;
 #pragma unroll
@@ -1065,15 +1091,17 @@ HX_API long long hx_paged_attention_scratch_floats_for(int dtype, int tokens, in
 
 // hx_paged_attention with kept first keys: a row at position p sees key j <= p when
 // p - j < window or j < keep_first (window 0: every earlier key, keep_first is then unused).
-HX_API int hx_paged_attention_kept(const void* q, int ldq, const void* k_cache, const void* v_cache,
-                                   int dtype, const int* positions, const int* token_request,
-                                   const int* request_table_row, const int* block_tables,
-                                   int table_stride, const int* request_start, int skip_query_len,
-                                   void* out, int ldo, float* partial, int* arrivals, int tokens,
-                                   int heads, int kv_heads, int head_dim, int page_size,
-                                   int num_pages, int window, int keep_first, float scale,
-                                   int split_keys, int max_splits, int* status,
-                                   cudaStream_t stream) {
+// ... and with the optional per-head sinks and distance slopes (see AttentionArgs; null: none).
+HX_API int hx_paged_attention_biased(const void* q, int ldq, const void* k_cache,
+                                     const void* v_cache, int dtype, const int* positions,
+                                     const int* token_request, const int* request_table_row,
+                                     const int* block_tables, int table_stride,
+                                     const int* request_start, int skip_query_len, void* out,
+                                     int ldo, float* partial, int* arrivals, int tokens, int heads,
+                                     int kv_heads, int head_dim, int page_size, int num_pages,
+                                     int window, int keep_first, float scale, int split_keys,
+                                     int max_splits, const float* sinks, const float* slopes,
+                                     int* status, cudaStream_t stream) {
   HX_REQUIRE(keep_first >= 0, "hx_paged_attention: keep_first must not be negative");
   if (window == 0) keep_first = 0;
   HX_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
@@ -1093,7 +1121,8 @@ HX_API int hx_paged_attention_kept(const void* q, int ldq, const void* k_cache, 
   AttentionArgs a{q, ldq, k_cache, v_cache, positions, token_request, request_table_row,
                   block_tables, table_stride, request_start, skip_query_len, out, ldo, partial,
                   arrivals, tokens, heads, kv_heads, head_dim, page_size, num_pages, window,
-                  keep_first, scale, split_keys, max_splits, status};
+                  keep_first, scale, split_keys, max_splits, status, sinks, slopes};
+  HX_REQUIRE(slopes == nullptr || scale != 0.0f, "hx_paged_attention: slopes need a scale");
   const long long items = static_cast<long long>(tokens) * heads * max_splits;
   HX_REQUIRE(items / STREAM_WARPS < (1ll << 31) - 1, "hx_paged_attention: grid too large");
   int rc;
@@ -1107,6 +1136,22 @@ HX_API int hx_paged_attention_kept(const void* q, int ldq, const void* k_cache, 
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_paged_attention");
   return HX_OK;
+}
+
+HX_API int hx_paged_attention_kept(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                   int dtype, const int* positions, const int* token_request,
+                                   const int* request_table_row, const int* block_tables,
+                                   int table_stride, const int* request_start, int skip_query_len,
+                                   void* out, int ldo, float* partial, int* arrivals, int tokens,
+                                   int heads, int kv_heads, int head_dim, int page_size,
+                                   int num_pages, int window, int keep_first, float scale,
+                                   int split_keys, int max_splits, int* status,
+                                   cudaStream_t stream) {
+  return hx_paged_attention_biased(q, ldq, k_cache, v_cache, dtype, positions, token_request,
+                                   request_table_row, block_tables, table_stride, request_start,
+                                   skip_query_len, out, ldo, partial, arrivals, tokens, heads,
+                                   kv_heads, head_dim, page_size, num_pages, window, keep_first,
+                                   scale, split_keys, max_splits, nullptr, nullptr, status, stream);
 }
 
 HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,

@@ -57,6 +57,11 @@ struct PrefillArgs {
                     // head, at most 64): its rows are the G heads of 64 / G tokens, token by
                     // token, so the heads that share keys and values read them once; the
                     // grid's second dimension then counts key/value heads
+  // Optional, per query head (null: absent).  sinks: the softmax's denominator also holds
+  // exp(sinks[h]), a term without key or value.  slopes: the score of key j for the query at
+  // position i is lowered by slopes[h] * (i - j).
+  const float* sinks = nullptr;
+  const float* slopes = nullptr;
 };
 
 constexpr int RING = 2;                         // key/value tiles in flight per CTA
@@ -239,6 +244,14 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
   const int q_pos1 = context + row0 + (warp_row + (lane >> 2) + 8) / pack;
   const int warp_pos_first = context + row0 + warp_row / pack;           // of the warp's 16 rows
   const int warp_pos_last = context + row0 + (warp_row + 15) / pack;
+  // heads of this lane's two rows (a packed tile's rows are a token's heads side by side)
+  const int row_head[2] = {head0 + (warp_row + (lane >> 2)) % pack,
+                           head0 + (warp_row + (lane >> 2) + 8) % pack};
+  float row_slope[2] = {0.0f, 0.0f};
+  if (a.slopes != nullptr) {
+    row_slope[0] = a.slopes[min(row_head[0], a.heads - 1)];
+    row_slope[1] = a.slopes[min(row_head[1], a.heads - 1)];
+  }
 
   for (int turn = 0; turn < n_tiles; ++turn) {
     const int tile = tile_at(turn);
@@ -307,6 +320,9 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float value = s[n][e] * a.scale;
+        if (a.slopes != nullptr)
+          value -= row_slope[e >> 1] *
+                   static_cast<float>(((e & 2) ? q_pos1 : q_pos0) - (key0 + n * 8 + (e & 1)));
         if (needs_mask) {
           const int key = key0 + n * 8 + (e & 1);
           const int q_pos = (e & 2) ? q_pos1 : q_pos0;
@@ -382,7 +398,16 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
     row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
     row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
   }
-  const float inverse[2] = {1.0f / row_sum[0], 1.0f / row_sum[1]};
+  float inverse[2] = {1.0f / row_sum[0], 1.0f / row_sum[1]};
+  if (a.sinks != nullptr) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float sink = a.sinks[min(row_head[r], a.heads - 1)];
+      const float top = fmaxf(row_max[r], sink);
+      const float keep = row_max[r] == -INFINITY ? 0.0f : __expf(row_max[r] - top);
+      inverse[r] = keep / (row_sum[r] * keep + __expf(sink - top));
+    }
+  }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = warp_row + (lane >> 2) + r * 8;
@@ -436,7 +461,8 @@ int prefill_attention(const void* q, int ldq, const void* k_cache,
                                          int ldo, int requests, int tile_bound, int heads,
                                          int kv_heads, int head_dim, int page_size, int num_pages,
                                          float scale, int min_query_len, int window,
-                                         int keep_first, int pack, int* status, cudaStream_t stream) {
+                                         int keep_first, int pack, int* status, cudaStream_t stream,
+                      const float* sinks = nullptr, const float* slopes = nullptr) {
   HX_REQUIRE(window >= 0 && keep_first >= 0, "hx_prefill_attention: bad window");
   if (window == 0) keep_first = 0;
   HX_REQUIRE(hx_prefill_attention_supports(head_dim, page_size),
@@ -458,7 +484,7 @@ int prefill_attention(const void* q, int ldq, const void* k_cache,
                 static_cast<const __nv_bfloat16*>(v_cache), request_start, request_context,
                 request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(out),
                 ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status,
-                window, keep_first, pack};
+                window, keep_first, pack, sinks, slopes};
   int rc = HX_ERR_UNSUPPORTED;
   switch (head_dim) {
     case 16: rc = launch<16>(a, tile_bound, stream); break;
@@ -535,4 +561,25 @@ HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, con
                                        request_table_row, block_tables, table_stride, out, ldo,
                                        requests, tile_bound, heads, kv_heads, head_dim, page_size,
                                        num_pages, scale, min_query_len, 0, 0, status, stream);
+}
+
+// The same with the optional per-head sinks and distance slopes (null: none); pack_heads != 0
+// takes the kernel whose rows are a token's heads (hx_prefill_attention_packed).
+HX_API int hx_prefill_attention_biased(const void* q, int ldq, const void* k_cache,
+                                       const void* v_cache, const int* request_start,
+                                       const int* request_context, const int* request_table_row,
+                                       const int* block_tables, int table_stride, void* out,
+                                       int ldo, int requests, int tile_bound, int heads,
+                                       int kv_heads, int head_dim, int page_size, int num_pages,
+                                       float scale, int min_query_len, int window,
+                                       int keep_first, int pack_heads, const float* sinks,
+                                       const float* slopes, int* status, cudaStream_t stream) {
+  HX_REQUIRE(!pack_heads || hx_prefill_attention_packed_tokens(heads, kv_heads) > 0,
+             "hx_prefill_attention_biased: %d heads on %d key/value heads do not pack", heads,
+             kv_heads);
+  return prefill_attention(q, ldq, k_cache, v_cache, request_start, request_context,
+                           request_table_row, block_tables, table_stride, out, ldo, requests,
+                           tile_bound, heads, kv_heads, head_dim, page_size, num_pages, scale,
+                           min_query_len, window, keep_first, pack_heads ? heads / kv_heads : 1,
+                           status, stream, sinks, slopes);
 }

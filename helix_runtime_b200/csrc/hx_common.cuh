@@ -229,7 +229,12 @@ __device__ __forceinline__ float hx_silu_fast(float x) {
 // projection.  gelu_tanh is GELU's tanh approximation, z/2 * (1 + tanh(u)) with
 // u = c (z + a z^3), c = sqrt(2/pi), a = 0.044715; since
 // 0.5 (1 + tanh(u)) = sigmoid(2u), it is z * sigmoid(2u) and shares the stable sigmoid.
-enum HxGateActivation : int { HX_GATE_SILU = 0, HX_GATE_GELU_TANH = 1 };
+// relu is max(z, 0).  The clamped form takes a limit L and is a function of gate AND up:
+// g = min(gate, L), u = clamp(up, -L, L), result g * sigmoid(1.702 g) * (u + 1).
+enum HxGateActivation : int {
+  HX_GATE_SILU = 0, HX_GATE_GELU_TANH = 1, HX_GATE_RELU = 2, HX_GATE_CLAMPED_SIGMOID = 3
+};
+constexpr float HX_CLAMPED_SIGMOID_SLOPE = 1.702f;
 
 __device__ __forceinline__ float hx_sigmoid(float x) {
   if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
@@ -253,4 +258,30 @@ __device__ __forceinline__ float hx_gate(float x, int activation) {
 
 __device__ __forceinline__ float hx_gate_fast(float x, int activation) {
   return activation == HX_GATE_GELU_TANH ? hx_gelu_tanh_fast(x) : hx_silu_fast(x);
+}
+
+// The gated product of a feed-forward for every HxGateActivation: f(gate) * up, or the clamped
+// form with its limit.
+__device__ __forceinline__ float hx_gated(float gate, float up, int activation, float limit) {
+  if (activation == HX_GATE_CLAMPED_SIGMOID) {
+    const float g = fminf(gate, limit);
+    const float u = fminf(fmaxf(up, -limit), limit);
+    return g * hx_sigmoid(HX_CLAMPED_SIGMOID_SLOPE * g) * (u + 1.0f);
+  }
+  if (activation == HX_GATE_RELU) return fmaxf(gate, 0.0f) * up;
+  return hx_gate(gate, activation) * up;
+}
+
+// The same with the hardware exponential, for results stored in bfloat16 right away.
+__device__ __forceinline__ float hx_gated_fast(float gate, float up, int activation, float limit) {
+  if (activation == HX_GATE_CLAMPED_SIGMOID) {
+    const float g = fminf(gate, limit);
+    const float u = fminf(fmaxf(up, -limit), limit);
+    const float v = HX_CLAMPED_SIGMOID_SLOPE * g;
+    const float gated = v >= 0.0f ? __fdividef(g, 1.0f + __expf(-v))
+                                  : __fdividef(g * __expf(v), 1.0f + __expf(v));
+    return gated * (u + 1.0f);
+  }
+  if (activation == HX_GATE_RELU) return fmaxf(gate, 0.0f) * up;
+  return hx_gate_fast(gate, activation) * up;
 }

@@ -37,7 +37,7 @@ void hx_count_launches(int kernels) { g_hx_launches.fetch_add(kernels, std::memo
 // counts once, when it is captured).
 HX_API long long hx_launch_count() { return g_hx_launches.load(std::memory_order_relaxed); }
 
-HX_API int hx_abi_version() { return 8; }
+HX_API int hx_abi_version() { return 9; }
 
 // Streaming multiprocessors of the current device (asked once per device); 0 with a message
 // when the device cannot be asked.  Launch sizes that should fill the GPU come from here.
@@ -465,8 +465,10 @@ HX_API int hx_layernorm(const float* x, const float* weight, const float* bias, 
 // (src/kernels/cuda/transformer.cu:68-83).  This is the path of the CUDA-core product;
 // the tensor-core product applies the same formula in its epilogue.
 template <typename TOut>
-__global__ void swiglu_kernel(float* __restrict__ gate_up, TOut* __restrict__ act, int tokens,
-                              int intermediate, int ld_in, int zero_input, int activation) {
+__global__ void swiglu_kernel(float* __restrict__ gate_up, const float* __restrict__ gate_bias,
+                              const float* __restrict__ up_bias, TOut* __restrict__ act, int tokens,
+                              int intermediate, int ld_in, int zero_input, int activation,
+                              float limit) {
   hx_pdl_prologue();
   const size_t total = static_cast<size_t>(tokens) * intermediate;
   for (size_t index = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; index < total;
@@ -474,7 +476,10 @@ __global__ void swiglu_kernel(float* __restrict__ gate_up, TOut* __restrict__ ac
     const size_t t = index / intermediate;
     const int i = static_cast<int>(index - t * intermediate);
     float* row = gate_up + t * ld_in;
-    act[index] = hx_from_float<TOut>(hx_gate(row[i], activation) * row[intermediate + i]);
+    float gate = row[i], up = row[intermediate + i];
+    if (gate_bias != nullptr) gate += gate_bias[i];
+    if (up_bias != nullptr) up += up_bias[i];
+    act[index] = hx_from_float<TOut>(hx_gated(gate, up, activation, limit));
     if (zero_input) {      // the buffer is a split-K accumulator: leave it clear for its next use
       row[i] = 0.0f;
       row[intermediate + i] = 0.0f;
@@ -482,11 +487,13 @@ __global__ void swiglu_kernel(float* __restrict__ gate_up, TOut* __restrict__ ac
   }
 }
 
-// activation: HX_GATE_SILU (SwiGLU) or HX_GATE_GELU_TANH.
-HX_API int hx_gated_activation(float* gate_up, void* act, int out_dtype, int tokens,
-                               int intermediate, int ld_in, int zero_input, int activation,
-                               cudaStream_t stream) {
-  HX_REQUIRE(activation == HX_GATE_SILU || activation == HX_GATE_GELU_TANH,
+// act[t, i] = f(gate_up[t, i] + gate_bias[i], gate_up[t, I + i] + up_bias[i]) for every
+// HxGateActivation (the biases may be null; `limit` belongs to HX_GATE_CLAMPED_SIGMOID).
+HX_API int hx_biased_gated_activation(float* gate_up, const float* gate_bias, const float* up_bias,
+                                      void* act, int out_dtype, int tokens, int intermediate,
+                                      int ld_in, int zero_input, int activation, float limit,
+                                      cudaStream_t stream) {
+  HX_REQUIRE(activation >= HX_GATE_SILU && activation <= HX_GATE_CLAMPED_SIGMOID,
              "hx_gated_activation: unknown activation %d", activation);
   HX_REQUIRE(tokens >= 0 && intermediate > 0 && ld_in >= 2 * intermediate, "hx_swiglu: bad sizes");
   if (tokens == 0) return HX_OK;
@@ -495,14 +502,27 @@ HX_API int hx_gated_activation(float* gate_up, void* act, int out_dtype, int tok
   const size_t resident = static_cast<size_t>(hx_device_sm_count() > 0 ? hx_device_sm_count() : 1) * 16;
   const int blocks = static_cast<int>(total / threads + 1 < resident ? total / threads + 1 : resident);
   if (out_dtype == HX_F32) {
-    hx_launch(swiglu_kernel<float>, blocks, threads, 0, stream, gate_up, static_cast<float*>(act), tokens, intermediate, ld_in, zero_input, activation);
+    hx_launch(swiglu_kernel<float>, blocks, threads, 0, stream, gate_up, gate_bias, up_bias,
+              static_cast<float*>(act), tokens, intermediate, ld_in, zero_input, activation, limit);
   } else if (out_dtype == HX_BF16) {
-    hx_launch(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream,  gate_up, static_cast<__nv_bfloat16*>(act), tokens, intermediate, ld_in, zero_input, activation);
+    hx_launch(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, gate_up, gate_bias, up_bias,
+              static_cast<__nv_bfloat16*>(act), tokens, intermediate, ld_in, zero_input, activation,
+              limit);
   } else {
     HX_REQUIRE(false, "hx_swiglu: unknown dtype %d", out_dtype);
   }
   HX_CHECK_LAUNCH("hx_swiglu");
   return HX_OK;
+}
+
+// activation: HX_GATE_SILU (SwiGLU), HX_GATE_GELU_TANH or HX_GATE_RELU.
+HX_API int hx_gated_activation(float* gate_up, void* act, int out_dtype, int tokens,
+                               int intermediate, int ld_in, int zero_input, int activation,
+                               cudaStream_t stream) {
+  HX_REQUIRE(activation != HX_GATE_CLAMPED_SIGMOID,
+             "hx_gated_activation: the clamped form needs its limit");
+  return hx_biased_gated_activation(gate_up, nullptr, nullptr, act, out_dtype, tokens,
+                                    intermediate, ld_in, zero_input, activation, 0.0f, stream);
 }
 
 HX_API int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int intermediate,

@@ -65,7 +65,7 @@ __device__ __forceinline__ void load_weight_box(void* dst, const CUtensorMap* ma
 template <int BN, int EPI>
 __device__ __forceinline__ void write_tile(void* out, int ldo, int tokens, int features,
                                            uint32_t lane_address, int feature, int token0,
-                                           int activation) {
+                                           int activation, float gate_limit) {
   const bool feature_ok = feature < features;
 #pragma unroll 1
   for (int column = 0; column < BN; column += 16) {
@@ -76,7 +76,7 @@ __device__ __forceinline__ void write_tile(void* out, int ldo, int tokens, int f
       float up[16];
       tmem_load16(lane_address + BN + column, up);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] = hx_gate_fast(acc[j], activation) * up[j];
+      for (int j = 0; j < 16; ++j) acc[j] = hx_gated_fast(acc[j], up[j], activation, gate_limit);
     }
     if (feature_ok) {
 #pragma unroll
@@ -139,6 +139,7 @@ struct GemmArgs {
   // The list lies in device memory and is written by an earlier kernel of the stream.
   const int* tile_group = nullptr;
   int group_rows = 0;
+  float gate_limit = 0.0f;    // gated epilogue: the limit of HX_GATE_CLAMPED_SIGMOID
 };
 
 template <int BN, int EPI>
@@ -275,7 +276,7 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
         tc_fence_after();
         const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         write_tile<BN, EPI>(args.out, args.ldo, args.tokens, args.features, lane_address, feature,
-                            token0, args.activation);
+                            token0, args.activation, args.gate_limit);
       }
     }
   }
@@ -369,6 +370,7 @@ struct PersistentArgs {
   // weight matrix; a unit of a tile with a negative group loads, multiplies and writes nothing.
   const int* tile_group;
   int group_rows;
+  float gate_limit = 0.0f;    // gated epilogue: the limit of HX_GATE_CLAMPED_SIGMOID
 };
 
 // What a CTA works on at a time: a tile, or (`partial`) a run of k-blocks of a tile that
@@ -449,7 +451,8 @@ __device__ __forceinline__ void load_row_into_accumulator(const float* out, int 
 // the accumulator.  With SwiGLU the accumulator holds 128 gate columns, then 128 up columns.
 template <int EPI>
 __device__ __forceinline__ void write_row(void* out, int ldo, int features, uint32_t lane_address,
-                                          int token, int tokens, int feature0, int activation) {
+                                          int token, int tokens, int feature0, int activation,
+                                          float gate_limit) {
   using Element = typename std::conditional<EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU,
                                             __nv_bfloat16, float>::type;
   constexpr int kColumns = EPI == EPI_SWIGLU ? BM : 2 * BM;
@@ -464,7 +467,7 @@ __device__ __forceinline__ void write_row(void* out, int ldo, int features, uint
       float up[16];
       tmem_load16(lane_address + BM + column, up);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] = hx_gate_fast(acc[j], activation) * up[j];
+      for (int j = 0; j < 16; ++j) acc[j] = hx_gated_fast(acc[j], up[j], activation, gate_limit);
     }
     if (token >= tokens) continue;
     Element* row = static_cast<Element*>(out) + static_cast<size_t>(token) * ldo + feature0 + column;
@@ -787,7 +790,7 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
         write_row<EPI>(args.out, args.ldo, args.features,
                        lane_base + buffer * Config::kBufferColumns,
                        unit.token_tile * BM + quarter * 32 + lane, args.tokens,
-                       unit.feature_tile * FEATURES, args.activation);
+                       unit.feature_tile * FEATURES, args.activation, args.gate_limit);
       }
       // every lane's tcgen05.ld has completed (the loads are waited for where they are
       // issued): hand the accumulator back
@@ -1094,16 +1097,11 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
 // kernel before this one on the stream.  `tokens` is the host's bound on the rows in use; rows
 // of tiles that are only partly in use are computed and stored like the others.  Epilogues 0,
 // 1 and 3 (5); `features` and `up_row_offset` count inside a group.
-HX_API int hx_gemm_tc_grouped(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
-                              int group_rows, int groups, void* out, int ldo, int tokens,
-                              int features, int depth, int epilogue, int up_row_offset,
-                              int token_tile, const int* tile_group, int* status,
-                              cudaStream_t stream) {
-  int activation = HX_GATE_SILU;
-  if (epilogue == 5) {
-    epilogue = EPI_SWIGLU;
-    activation = HX_GATE_GELU_TANH;
-  }
+static int gemm_tc_grouped(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                           int group_rows, int groups, void* out, int ldo, int tokens,
+                           int features, int depth, int epilogue, int activation,
+                           float gate_limit, int up_row_offset, int token_tile,
+                           const int* tile_group, int* status, cudaStream_t stream) {
   HX_REQUIRE(groups > 0 && group_rows > 0 && tile_group != nullptr,
              "hx_gemm_tc_grouped: bad groups");
   HX_REQUIRE(static_cast<long long>(groups) * group_rows < (1ll << 31),
@@ -1136,14 +1134,14 @@ HX_API int hx_gemm_tc_grouped(const void* x, int ldx, int x_capacity_rows, const
     // tiles of 128 tokens: the persistent kernel, as for prompt portions of a plain product
     PersistentArgs persistent{out, ldo, tokens, features, depth, up_row_offset, 0, 0, 0,
                               total_k_blocks, status, RopeArgs{}, -1, activation, tile_group,
-                              group_rows};
+                              group_rows, gate_limit};
     rc = launch_persistent_epilogue(epilogue, map_w, map_x, persistent, stream);
     if (rc != HX_OK) return rc;
     HX_CHECK_LAUNCH("hx_gemm_tc_grouped");
     return HX_OK;
   }
   GemmArgs args{out, ldo, tokens, features, depth, up_row_offset, total_k_blocks, 0, status,
-                activation, tile_group, group_rows};
+                activation, tile_group, group_rows, gate_limit};
   const dim3 grid((tokens + token_tile - 1) / token_tile, (features + BM - 1) / BM, 1);
   HX_REQUIRE(grid.y <= 65535, "hx_gemm_tc_grouped: too many features (%d)", features);
   switch (token_tile) {
@@ -1156,6 +1154,36 @@ HX_API int hx_gemm_tc_grouped(const void* x, int ldx, int x_capacity_rows, const
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_gemm_tc_grouped");
   return HX_OK;
+}
+
+HX_API int hx_gemm_tc_grouped(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                              int group_rows, int groups, void* out, int ldo, int tokens,
+                              int features, int depth, int epilogue, int up_row_offset,
+                              int token_tile, const int* tile_group, int* status,
+                              cudaStream_t stream) {
+  int activation = HX_GATE_SILU;
+  if (epilogue == 5) {
+    epilogue = EPI_SWIGLU;
+    activation = HX_GATE_GELU_TANH;
+  }
+  return gemm_tc_grouped(x, ldx, x_capacity_rows, w, ldw, group_rows, groups, out, ldo, tokens,
+                         features, depth, epilogue, activation, 0.0f, up_row_offset, token_tile,
+                         tile_group, status, stream);
+}
+
+// The grouped product with the gated epilogue for any HxGateActivation: out = f(gate, up) with
+// the gate rows at 0 and the up rows at up_row_offset inside a group; gate_limit is the limit of
+// HX_GATE_CLAMPED_SIGMOID.
+HX_API int hx_gemm_tc_grouped_gated(const void* x, int ldx, int x_capacity_rows, const void* w,
+                                    int ldw, int group_rows, int groups, void* out, int ldo,
+                                    int tokens, int features, int depth, int activation,
+                                    float gate_limit, int up_row_offset, int token_tile,
+                                    const int* tile_group, int* status, cudaStream_t stream) {
+  HX_REQUIRE(activation >= HX_GATE_SILU && activation <= HX_GATE_CLAMPED_SIGMOID,
+             "hx_gemm_tc_grouped_gated: unknown activation %d", activation);
+  return gemm_tc_grouped(x, ldx, x_capacity_rows, w, ldw, group_rows, groups, out, ldo, tokens,
+                         features, depth, EPI_SWIGLU, activation, gate_limit, up_row_offset,
+                         token_tile, tile_group, status, stream);
 }
 
 // Fewest tokens hx_gemm_tc_rope_append takes: it exists for the persistent kernel only.

@@ -14,6 +14,8 @@
 //     the head's latent part in that buffer, zeros to the row's end.
 //
 // Norms, angles and rotations are float32 (the float32 engine takes the angle in double).
+// `amplitude` multiplies sine and cosine (1 unless the frequencies are stretched for contexts
+// beyond the trained length; the stretched frequencies themselves come from the host).
 #include "hx_common.cuh"
 
 namespace {
@@ -34,7 +36,8 @@ __device__ __forceinline__ void angle_of(int position, int pair, const float* fr
 // coordinate e of `rot` coordinates, of which the first `dims` are rotated in pairs
 template <bool EXACT, typename Load>
 __device__ __forceinline__ float rotated(Load load, int e, int dims, int layout, int position,
-                                         const float* freq, const double* freq_exact) {
+                                         const float* freq, const double* freq_exact,
+                                         float amplitude) {
   const float x = load(e);
   if (e >= dims) return x;
   int pair, partner;
@@ -49,6 +52,8 @@ __device__ __forceinline__ float rotated(Load load, int e, int dims, int layout,
   }
   float sine, cosine;
   angle_of<EXACT>(position, pair, freq, freq_exact, sine, cosine);
+  sine *= amplitude;        // 1 unless the frequencies are stretched
+  cosine *= amplitude;
   const float y = load(partner);
   return leads ? x * cosine - y * sine : x * cosine + y * sine;
 }
@@ -69,6 +74,7 @@ struct LatentPrepareArgs {
   T* rows;                  // [tokens, ld_rows]: the key row at key_offset, the value row behind it
   int ld_rows, key_offset;
   int q_rank, kv_rank, rot, row_dim;
+  float amplitude;          // factor on sine and cosine
 };
 
 template <typename T>
@@ -101,7 +107,7 @@ __global__ __launch_bounds__(128) void latent_prepare_kernel(const LatentPrepare
       k = v = hx_to_float<T>(hx_from_float<T>(kv[c] * kv_inverse * a.kv_weight[c]));
     } else if (c < a.kv_rank + a.rot) {
       k = rotated<EXACT>([&](int e) { return shared_part[e]; }, c - a.kv_rank, a.rotary_dims,
-                         a.layout, position, a.freq, a.freq_exact);
+                         a.layout, position, a.freq, a.freq_exact, a.amplitude);
     }
     key[c] = hx_from_float<T>(k);
     value[c] = hx_from_float<T>(v);
@@ -115,7 +121,7 @@ __global__ __launch_bounds__(64) void latent_queries_kernel(
     const T* __restrict__ q, int ld_q, int rot_offset, T* __restrict__ rows, int ld_rows,
     const int* __restrict__ positions, const float* __restrict__ freq,
     const double* __restrict__ freq_exact, int rotary_dims, int layout, int kv_rank, int rot,
-    int row_dim) {
+    int row_dim, float amplitude) {
   constexpr bool EXACT = sizeof(T) == 4;
   hx_pdl_prologue();
   const int token = blockIdx.x;
@@ -127,7 +133,7 @@ __global__ __launch_bounds__(64) void latent_queries_kernel(
     float v = 0.0f;
     if (c < kv_rank + rot)
       v = rotated<EXACT>([&](int e) { return hx_to_float<T>(part[e]); }, c - kv_rank, rotary_dims,
-                         layout, position, freq, freq_exact);
+                         layout, position, freq, freq_exact, amplitude);
     row[c] = hx_from_float<T>(v);
   }
 }
@@ -139,7 +145,7 @@ HX_API int hx_latent_prepare(const float* down, int ld_down, const float* q_weig
                              const float* freq, const double* freq_exact, int rotary_dims,
                              int layout, void* query_latent, int ld_latent, void* rows, int ld_rows,
                              int key_offset, int dtype, int tokens, int q_rank, int kv_rank, int rot,
-                             int row_dim, cudaStream_t stream) {
+                             int row_dim, float amplitude, cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && q_rank > 0 && kv_rank > 0 && rot >= 0 && row_dim >= kv_rank + rot,
              "hx_latent_prepare: bad sizes");
   HX_REQUIRE(ld_down >= q_rank + kv_rank + rot && ld_latent >= q_rank &&
@@ -154,14 +160,14 @@ HX_API int hx_latent_prepare(const float* down, int ld_down, const float* q_weig
     LatentPrepareArgs<float> a{down, ld_down, q_weight, kv_weight, eps, positions, freq, freq_exact,
                                rotary_dims, layout, static_cast<float*>(query_latent), ld_latent,
                                static_cast<float*>(rows), ld_rows, key_offset, q_rank, kv_rank, rot,
-                               row_dim};
+                               row_dim, amplitude};
     hx_launch(latent_prepare_kernel<float>, dim3(tokens), 128, 0, stream, a);
   } else if (dtype == HX_BF16) {
     LatentPrepareArgs<__nv_bfloat16> a{down, ld_down, q_weight, kv_weight, eps, positions, freq,
                                        freq_exact, rotary_dims, layout,
                                        static_cast<__nv_bfloat16*>(query_latent), ld_latent,
                                        static_cast<__nv_bfloat16*>(rows), ld_rows, key_offset,
-                                       q_rank, kv_rank, rot, row_dim};
+                                       q_rank, kv_rank, rot, row_dim, amplitude};
     hx_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(tokens), 128, 0, stream, a);
   } else {
     HX_REQUIRE(false, "hx_latent_prepare: unknown dtype %d", dtype);
@@ -173,7 +179,8 @@ HX_API int hx_latent_prepare(const float* down, int ld_down, const float* q_weig
 HX_API int hx_latent_queries(const void* q, int ld_q, int rot_offset, void* rows, int ld_rows,
                              const int* positions, const float* freq, const double* freq_exact,
                              int rotary_dims, int layout, int dtype, int tokens, int heads,
-                             int kv_rank, int rot, int row_dim, cudaStream_t stream) {
+                             int kv_rank, int rot, int row_dim, float amplitude,
+                             cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && heads > 0 && kv_rank > 0 && rot >= 0 && row_dim >= kv_rank + rot,
              "hx_latent_queries: bad sizes");
   HX_REQUIRE(ld_q >= rot_offset + heads * rot && ld_rows >= heads * row_dim,
@@ -185,12 +192,12 @@ HX_API int hx_latent_queries(const void* q, int ld_q, int rot_offset, void* rows
   if (dtype == HX_F32) {
     hx_launch(latent_queries_kernel<float>, grid, 64, 0, stream, static_cast<const float*>(q), ld_q,
               rot_offset, static_cast<float*>(rows), ld_rows, positions, freq, freq_exact,
-              rotary_dims, layout, kv_rank, rot, row_dim);
+              rotary_dims, layout, kv_rank, rot, row_dim, amplitude);
   } else if (dtype == HX_BF16) {
     hx_launch(latent_queries_kernel<__nv_bfloat16>, grid, 64, 0, stream,
               static_cast<const __nv_bfloat16*>(q), ld_q, rot_offset,
               static_cast<__nv_bfloat16*>(rows), ld_rows, positions, freq, freq_exact, rotary_dims,
-              layout, kv_rank, rot, row_dim);
+              layout, kv_rank, rot, row_dim, amplitude);
   } else {
     HX_REQUIRE(false, "hx_latent_queries: unknown dtype %d", dtype);
   }

@@ -1,0 +1,288 @@
+// Norms that sit between a product and what follows it, one CTA per token, float32 throughout:
+//
+//   * hx_norm_residual_add: a sublayer whose output passes an RMS norm BEFORE it joins the
+//     residual, x += mult * y / sqrt(mean(y^2) + eps) * w; optionally the updated row is also
+//     written in the compute type (the input of a product that reads the residual itself);
+//   * hx_biased_normed_rows: what an attention layer does to its fused projection
+//     [q | k | v | head gates] before the cache append: biases, ONE RMS norm over all of a
+//     token's query coordinates and one over all of its key coordinates (not per head), a
+//     factor on the query that grows with the logarithm of the position, values blended with
+//     the values an earlier layer computed for the same token, and the sigmoid of the head
+//     gates' sums; queries, keys and values leave in rows of row_dim per head (zeros behind
+//     the head's own coordinates);
+//   * hx_head_gate: every head of the attention's result times its token's gate;
+//   * hx_token_gate: g = gelu_tanh(s) * table[token][offset + c], the gate of a per-token
+//     input that is looked up in a table by the token's id.
+#include "hx_common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ __launch_bounds__(256) void norm_residual_add_kernel(
+    float* __restrict__ residual, const float* __restrict__ y, const float* __restrict__ weight,
+    float eps, float mult, T* __restrict__ cast_out, int ld_cast, int width) {
+  __shared__ float scratch[32];
+  hx_pdl_prologue();
+  const size_t row = static_cast<size_t>(blockIdx.x) * width;
+  float sum = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) sum = fmaf(y[row + c], y[row + c], sum);
+  const float inverse =
+      mult / sqrtf(hx_block_sum(sum, scratch) / static_cast<float>(width) + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float x = fmaf(y[row + c] * inverse, weight[c], residual[row + c]);
+    residual[row + c] = x;
+    if (cast_out != nullptr)
+      cast_out[static_cast<size_t>(blockIdx.x) * ld_cast + c] = hx_from_float<T>(x);
+  }
+}
+
+template <typename T>
+struct NormedRowsArgs {
+  float* projected;            // [tokens, ld_projected]: q | k | v | head gates
+  int ld_projected;
+  int clear;                   // 1: the buffer is an accumulator, leave it zero
+  const float* q_bias;         // [heads * head_dim] or null
+  const float* k_bias;         // [kv_heads * head_dim] or null
+  const float* v_bias;         // [kv_heads * value_dim] or null
+  const float* q_weight;       // [heads * head_dim] or null: no norm
+  const float* k_weight;       // [kv_heads * head_dim] or null
+  float eps;
+  const int* positions;
+  float temp_coef;             // query factor 1 + coef * ln(floor((p + 1) / every) + 1)
+  int temp_every;              // 0: none
+  int value_mix;               // 0: none; 1: this layer's values are kept as the source;
+                               // 2: v <- (1 - lambda) v + lambda source
+  float lambda;
+  float* value_source;         // [tokens, kv_heads * value_dim]
+  T* rows;                     // [tokens, ld_rows]: heads | kv_heads | kv_heads rows of row_dim
+  int ld_rows;
+  float* gates;                // [tokens, heads]: sigmoid of the gate sums; null: none
+  int heads, kv_heads, head_dim, value_dim, row_dim;
+};
+
+template <typename T>
+__global__ __launch_bounds__(256) void biased_normed_rows_kernel(const NormedRowsArgs<T> a) {
+  __shared__ float scratch[32];
+  hx_pdl_prologue();
+  const int token = blockIdx.x;
+  float* in = a.projected + static_cast<size_t>(token) * a.ld_projected;
+  T* out = a.rows + static_cast<size_t>(token) * a.ld_rows;
+  const int q_size = a.heads * a.head_dim;
+  const int k_size = a.kv_heads * a.head_dim;
+  const int v_size = a.kv_heads * a.value_dim;
+  auto biased = [&](int c, const float* bias, int base) {
+    return in[base + c] + (bias != nullptr ? bias[c] : 0.0f);
+  };
+  float q_inverse = 1.0f, k_inverse = 1.0f;
+  if (a.q_weight != nullptr) {
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < q_size; c += blockDim.x) {
+      const float v = biased(c, a.q_bias, 0);
+      sum = fmaf(v, v, sum);
+    }
+    q_inverse = 1.0f / sqrtf(hx_block_sum(sum, scratch) / static_cast<float>(q_size) + a.eps);
+  }
+  if (a.k_weight != nullptr) {
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < k_size; c += blockDim.x) {
+      const float v = biased(c, a.k_bias, q_size);
+      sum = fmaf(v, v, sum);
+    }
+    k_inverse = 1.0f / sqrtf(hx_block_sum(sum, scratch) / static_cast<float>(k_size) + a.eps);
+  }
+  float temperature = 1.0f;
+  if (a.temp_every > 0)
+    temperature = 1.0f + a.temp_coef *
+        logf(static_cast<float>((a.positions[token] + 1) / a.temp_every) + 1.0f);
+  const int D = a.head_dim, R = a.row_dim, E = a.value_dim;
+  // queries
+  for (int c = threadIdx.x; c < a.heads * R; c += blockDim.x) {
+    const int head = c / R, d = c - head * R;
+    float v = 0.0f;
+    if (d < D) {
+      const int i = head * D + d;
+      v = biased(i, a.q_bias, 0) * q_inverse;
+      if (a.q_weight != nullptr) v *= a.q_weight[i];
+      v *= temperature;
+    }
+    out[c] = hx_from_float<T>(v);
+  }
+  // keys, then values
+  T* keys = out + a.heads * R;
+  T* values = keys + a.kv_heads * R;
+  float* source = a.value_source == nullptr ? nullptr
+                                            : a.value_source + static_cast<size_t>(token) * v_size;
+  for (int c = threadIdx.x; c < a.kv_heads * R; c += blockDim.x) {
+    const int head = c / R, d = c - head * R;
+    float k = 0.0f, v = 0.0f;
+    if (d < D) {
+      const int i = head * D + d;
+      k = biased(i, a.k_bias, q_size) * k_inverse;
+      if (a.k_weight != nullptr) k *= a.k_weight[i];
+    }
+    if (d < E) {
+      const int i = head * E + d;
+      v = biased(i, a.v_bias, q_size + k_size);
+      if (a.value_mix == 1) {
+        source[i] = v;
+      } else if (a.value_mix == 2) {
+        v = (1.0f - a.lambda) * v + a.lambda * source[i];
+      }
+    }
+    keys[c] = hx_from_float<T>(k);
+    values[c] = hx_from_float<T>(v);
+  }
+  if (a.gates != nullptr)
+    for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
+      a.gates[static_cast<size_t>(token) * a.heads + h] =
+          hx_sigmoid(in[q_size + k_size + v_size + h]);
+  if (a.clear) {
+    __syncthreads();
+    const int used = q_size + k_size + v_size + (a.gates != nullptr ? a.heads : 0);
+    for (int c = threadIdx.x; c < used; c += blockDim.x) in[c] = 0.0f;
+  }
+}
+
+// grid (tokens, heads)
+template <typename T>
+__global__ __launch_bounds__(64) void head_gate_kernel(T* __restrict__ context, int ld_context,
+                                                       const float* __restrict__ gates,
+                                                       int heads, int row_dim) {
+  hx_pdl_prologue();
+  const int token = blockIdx.x, head = blockIdx.y;
+  const float gate = gates[static_cast<size_t>(token) * heads + head];
+  T* row = context + static_cast<size_t>(token) * ld_context + head * row_dim;
+  for (int c = threadIdx.x; c < row_dim; c += blockDim.x)
+    row[c] = hx_from_float<T>(hx_to_float<T>(row[c]) * gate);
+}
+
+// grid (tokens)
+template <typename T>
+__global__ __launch_bounds__(128) void token_gate_kernel(
+    float* __restrict__ sums, int ld_sums, int clear, const T* __restrict__ table, int ld_table,
+    int offset, int vocab, const int* __restrict__ token_ids, T* __restrict__ out, int ld_out,
+    int dim, int* __restrict__ status) {
+  hx_pdl_prologue();
+  const int token = blockIdx.x;
+  int id = token_ids[token];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && status != nullptr) atomicOr(status, HX_FLAG_BAD_TOKEN);
+    id = 0;
+  }
+  float* s = sums + static_cast<size_t>(token) * ld_sums;
+  const T* e = table + static_cast<size_t>(id) * ld_table + offset;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    out[static_cast<size_t>(token) * ld_out + c] =
+        hx_from_float<T>(hx_gelu_tanh(s[c]) * hx_to_float<T>(e[c]));
+    if (clear) s[c] = 0.0f;
+  }
+}
+
+}  // namespace
+
+// residual[:tokens] += mult * y / sqrt(mean(y^2) + eps) * weight, float32 rows [tokens, width]
+// contiguous; cast_out (may be null): the updated rows in `dtype`, row stride ld_cast.
+HX_API int hx_norm_residual_add(float* residual, const float* y, const float* weight, float eps,
+                                float mult, void* cast_out, int ld_cast, int dtype, int tokens,
+                                int width, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && width > 0 && eps > 0.0f, "hx_norm_residual_add: bad sizes");
+  HX_REQUIRE(cast_out == nullptr || ld_cast >= width, "hx_norm_residual_add: bad stride");
+  if (tokens == 0) return HX_OK;
+  if (dtype == HX_F32) {
+    hx_launch(norm_residual_add_kernel<float>, dim3(tokens), 256, 0, stream, residual, y, weight,
+              eps, mult, static_cast<float*>(cast_out), ld_cast, width);
+  } else if (dtype == HX_BF16) {
+    hx_launch(norm_residual_add_kernel<__nv_bfloat16>, dim3(tokens), 256, 0, stream, residual, y,
+              weight, eps, mult, static_cast<__nv_bfloat16*>(cast_out), ld_cast, width);
+  } else {
+    HX_REQUIRE(false, "hx_norm_residual_add: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_norm_residual_add");
+  return HX_OK;
+}
+
+// projected float32 [tokens, ld_projected] = [heads * head_dim | kv_heads * head_dim | kv_heads *
+// value_dim | heads gate sums (when gates is not null)]; rows [tokens, ld_rows] in `dtype` =
+// [heads | kv_heads | kv_heads] rows of row_dim.  See NormedRowsArgs for the rest.
+HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
+                                 const float* q_bias, const float* k_bias, const float* v_bias,
+                                 const float* q_weight, const float* k_weight, float eps,
+                                 const int* positions, float temp_coef, int temp_every,
+                                 int value_mix, float lambda, float* value_source, void* rows,
+                                 int ld_rows, float* gates, int dtype, int tokens, int heads,
+                                 int kv_heads, int head_dim, int value_dim, int row_dim,
+                                 cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && head_dim > 0 && value_dim > 0 &&
+                 row_dim >= head_dim && row_dim >= value_dim,
+             "hx_biased_normed_rows: bad sizes");
+  HX_REQUIRE(ld_projected >= heads * head_dim + kv_heads * (head_dim + value_dim) +
+                                 (gates != nullptr ? heads : 0) &&
+                 ld_rows >= (heads + 2 * kv_heads) * row_dim,
+             "hx_biased_normed_rows: bad strides");
+  HX_REQUIRE(value_mix >= 0 && value_mix <= 2 && (value_mix == 0 || value_source != nullptr),
+             "hx_biased_normed_rows: value mixing needs its source buffer");
+  HX_REQUIRE(temp_every >= 0 && (temp_every == 0 || positions != nullptr) &&
+                 ((q_weight == nullptr && k_weight == nullptr) || eps > 0.0f),
+             "hx_biased_normed_rows: bad constants");
+  if (tokens == 0) return HX_OK;
+  if (dtype == HX_F32) {
+    NormedRowsArgs<float> a{projected, ld_projected, clear, q_bias, k_bias, v_bias, q_weight,
+                            k_weight, eps, positions, temp_coef, temp_every, value_mix, lambda,
+                            value_source, static_cast<float*>(rows), ld_rows, gates, heads,
+                            kv_heads, head_dim, value_dim, row_dim};
+    hx_launch(biased_normed_rows_kernel<float>, dim3(tokens), 256, 0, stream, a);
+  } else if (dtype == HX_BF16) {
+    NormedRowsArgs<__nv_bfloat16> a{projected, ld_projected, clear, q_bias, k_bias, v_bias,
+                                    q_weight, k_weight, eps, positions, temp_coef, temp_every,
+                                    value_mix, lambda, value_source,
+                                    static_cast<__nv_bfloat16*>(rows), ld_rows, gates, heads,
+                                    kv_heads, head_dim, value_dim, row_dim};
+    hx_launch(biased_normed_rows_kernel<__nv_bfloat16>, dim3(tokens), 256, 0, stream, a);
+  } else {
+    HX_REQUIRE(false, "hx_biased_normed_rows: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_biased_normed_rows");
+  return HX_OK;
+}
+
+// context[t][h * row_dim + c] *= gates[t][h]; context in `dtype`, gates float32 [tokens, heads].
+HX_API int hx_head_gate(void* context, int ld_context, const float* gates, int dtype, int tokens,
+                        int heads, int row_dim, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && heads > 0 && heads <= 65535 && row_dim > 0 &&
+                 ld_context >= heads * row_dim, "hx_head_gate: bad sizes");
+  if (tokens == 0) return HX_OK;
+  if (dtype == HX_F32) {
+    hx_launch(head_gate_kernel<float>, dim3(tokens, heads), 64, 0, stream,
+              static_cast<float*>(context), ld_context, gates, heads, row_dim);
+  } else if (dtype == HX_BF16) {
+    hx_launch(head_gate_kernel<__nv_bfloat16>, dim3(tokens, heads), 64, 0, stream,
+              static_cast<__nv_bfloat16*>(context), ld_context, gates, heads, row_dim);
+  } else {
+    HX_REQUIRE(false, "hx_head_gate: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_head_gate");
+  return HX_OK;
+}
+
+// out[t][c] = gelu_tanh(sums[t][c]) * table[token_ids[t]][offset + c] for c < dim; sums float32
+// (cleared when `clear`), table and out in `dtype`.
+HX_API int hx_token_gate(float* sums, int ld_sums, int clear, const void* table, int ld_table,
+                         int offset, int vocab, const int* token_ids, void* out, int ld_out,
+                         int dtype, int tokens, int dim, int* status, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && dim > 0 && ld_sums >= dim && ld_out >= dim && offset >= 0 &&
+                 ld_table >= offset + dim && vocab > 0, "hx_token_gate: bad sizes");
+  if (tokens == 0) return HX_OK;
+  if (dtype == HX_F32) {
+    hx_launch(token_gate_kernel<float>, dim3(tokens), 128, 0, stream, sums, ld_sums, clear,
+              static_cast<const float*>(table), ld_table, offset, vocab, token_ids,
+              static_cast<float*>(out), ld_out, dim, status);
+  } else if (dtype == HX_BF16) {
+    hx_launch(token_gate_kernel<__nv_bfloat16>, dim3(tokens), 128, 0, stream, sums, ld_sums,
+              clear, static_cast<const __nv_bfloat16*>(table), ld_table, offset, vocab, token_ids,
+              static_cast<__nv_bfloat16*>(out), ld_out, dim, status);
+  } else {
+    HX_REQUIRE(false, "hx_token_gate: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_token_gate");
+  return HX_OK;
+}

@@ -17,45 +17,74 @@ namespace {
 
 constexpr int ROUTE_MAX_PER_LANE = 32;      // experts a lane can mark as taken: 1,024 in all
 
+// What the router's sums become, and what is chosen by and weighted with.
+struct RouteRule {
+  int softmax;                // 0: s = sigmoid(z); 1: s = softmax(z) over all outputs
+  const float* correction;    // [experts] added to s for the CHOICE only; may be null
+  int normalize;              // 1: weights s / (sum of the chosen + 1e-20) * scale; 0: s * scale
+};
+
 __global__ __launch_bounds__(128) void route_top_kernel(const float* __restrict__ sums, int ld,
                                                         int tokens, int experts, int top,
-                                                        float scale, int* __restrict__ chosen,
+                                                        float scale, RouteRule rule,
+                                                        int* __restrict__ chosen,
                                                         float* __restrict__ weights) {
   hx_pdl_prologue();
   const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (token >= tokens) return;
   const int lane = threadIdx.x & 31;
   const float* z = sums + static_cast<size_t>(token) * ld;
+  // softmax: the row's maximum and the sum of exp(z - max), in ascending order per lane
+  float row_max = 0.0f, inverse_sum = 1.0f;
+  if (rule.softmax) {
+    row_max = -INFINITY;
+    for (int e = lane; e < experts; e += 32) row_max = fmaxf(row_max, z[e]);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      row_max = fmaxf(row_max, __shfl_xor_sync(0xffffffffu, row_max, offset));
+    float sum = 0.0f;
+    for (int e = lane; e < experts; e += 32) sum += expf(z[e] - row_max);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+      sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+    inverse_sum = 1.0f / sum;
+  }
+  auto score_of = [&](int e) {
+    return rule.softmax ? expf(z[e] - row_max) * inverse_sum : hx_sigmoid(z[e]);
+  };
   unsigned taken = 0u;          // bit i: expert lane + 32 i is chosen already
   float total = 0.0f;
   for (int k = 0; k < top; ++k) {
-    float best = -1.0f;         // scores lie in [0, 1]
+    float best = -INFINITY, best_score = 0.0f;
     int best_index = 0x7fffffff;
     for (int i = 0, e = lane; e < experts; ++i, e += 32) {
       if (taken & (1u << i)) continue;
-      const float s = hx_sigmoid(z[e]);
-      if (s > best) { best = s; best_index = e; }      // ascending e: the first of equals stays
+      const float s = score_of(e);
+      const float c = rule.correction != nullptr ? s + rule.correction[e] : s;
+      if (c > best) { best = c; best_score = s; best_index = e; }   // the first of equals stays
     }
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) {
       const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const float other_score = __shfl_xor_sync(0xffffffffu, best_score, offset);
       const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
       if (other > best || (other == best && other_index < best_index)) {
         best = other;
+        best_score = other_score;
         best_index = other_index;
       }
     }
     if ((best_index & 31) == lane && best_index < experts) taken |= 1u << (best_index >> 5);
-    total += best;
+    total += best_score;
     if (lane == 0) {
       chosen[static_cast<size_t>(token) * top + k] = best_index;
-      weights[static_cast<size_t>(token) * top + k] = best;
+      weights[static_cast<size_t>(token) * top + k] = best_score;
     }
   }
   __syncwarp();
   if (lane < top) {
     float* w = weights + static_cast<size_t>(token) * top + lane;
-    *w = *w / (total + 1e-20f) * scale;
+    *w = rule.normalize ? *w / (total + 1e-20f) * scale : *w * scale;
   }
 }
 
@@ -118,7 +147,7 @@ constexpr int DOWN_ROWS = 32;         // output rows a CTA of the second product
 template <typename T>
 __global__ __launch_bounds__(EXPERT_WARPS * 32) void expert_gate_up_kernel(
     const T* __restrict__ x, int ld_x, const T* __restrict__ gate_up, const int* __restrict__ chosen,
-    T* __restrict__ act, int top, int ff, int width, int experts, int activation) {
+    T* __restrict__ act, int top, int ff, int width, int experts, int activation, float limit) {
   extern __shared__ float4 shared4[];
   float* xs = reinterpret_cast<float*>(shared4);
   hx_pdl_prologue();
@@ -136,7 +165,7 @@ __global__ __launch_bounds__(EXPERT_WARPS * 32) void expert_gate_up_kernel(
     const float g = warp_sum(lane_dot<T>(w + static_cast<size_t>(j) * width, xs, width, lane));
     const float u = warp_sum(lane_dot<T>(w + static_cast<size_t>(ff + j) * width, xs, width, lane));
     if (lane == 0)
-      act[static_cast<size_t>(pair) * ff + j] = hx_from_float<T>(hx_gate(g, activation) * u);
+      act[static_cast<size_t>(pair) * ff + j] = hx_from_float<T>(hx_gated(g, u, activation, limit));
   }
 }
 
@@ -291,28 +320,59 @@ __global__ __launch_bounds__(128) void expert_combine_kernel(
   }
 }
 
+// grid (ceil(width / 512), tokens): out[t][c] += x[t][c] * (sum of the weights of the token's
+// choices that name no expert with matrices: index >= experts is an identity output)
+template <typename T>
+__global__ __launch_bounds__(128) void expert_identity_kernel(
+    const T* __restrict__ x, int ld_x, const int* __restrict__ chosen,
+    const float* __restrict__ weights, float* __restrict__ out, int ld_out, int top, int width,
+    int experts) {
+  hx_pdl_prologue();
+  const int token = blockIdx.y;
+  float weight = 0.0f;
+  for (int k = 0; k < top; ++k)
+    if (chosen[token * top + k] >= experts) weight += weights[token * top + k];
+  if (weight == 0.0f) return;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  for (int c = c0; c < c0 + 4 && c < width; ++c)
+    out[static_cast<size_t>(token) * ld_out + c] =
+        fmaf(weight, hx_to_float<T>(x[static_cast<size_t>(token) * ld_x + c]),
+             out[static_cast<size_t>(token) * ld_out + c]);
+}
+
 }  // namespace
 
 // sums float32 [tokens, ld] (the router's products); chosen int32 and weights float32
-// [tokens, top].
-HX_API int hx_route_top(const float* sums, int ld, int tokens, int experts, int top, float scale,
-                        int* chosen, float* weights, cudaStream_t stream) {
+// [tokens, top].  softmax: scores are softmax(z) over all `experts` outputs instead of
+// sigmoid(z); correction [experts] (may be null) is added to the scores for the choice only;
+// normalize 0: the weights are the chosen scores times scale, not divided by their sum.
+HX_API int hx_route_top_ruled(const float* sums, int ld, int tokens, int experts, int top,
+                              float scale, int softmax, const float* correction, int normalize,
+                              int* chosen, float* weights, cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts && ld >= experts,
              "hx_route_top: bad sizes");
   HX_REQUIRE(experts <= 32 * ROUTE_MAX_PER_LANE && top <= 32,
              "hx_route_top: at most %d experts and 32 choices", 32 * ROUTE_MAX_PER_LANE);
   if (tokens == 0) return HX_OK;
+  const RouteRule rule{softmax, correction, normalize};
   hx_launch(route_top_kernel, dim3((tokens + 3) / 4), 128, 0, stream, sums, ld, tokens, experts,
-            top, scale, chosen, weights);
+            top, scale, rule, chosen, weights);
   HX_CHECK_LAUNCH("hx_route_top");
   return HX_OK;
 }
 
+// s = sigmoid(z), the `top` largest, weights s / (sum of the chosen + 1e-20) * scale.
+HX_API int hx_route_top(const float* sums, int ld, int tokens, int experts, int top, float scale,
+                        int* chosen, float* weights, cudaStream_t stream) {
+  return hx_route_top_ruled(sums, ld, tokens, experts, top, scale, 0, nullptr, 1, chosen, weights,
+                            stream);
+}
+
 // x [tokens, ld_x], gate_up [experts, 2 * ff, width] (gate rows, then up rows), act
 // [tokens * top, ff], all in the compute dtype; chosen int32 [tokens, top].
-HX_API int hx_expert_gate_up(const void* x, int ld_x, const void* gate_up, const int* chosen,
+HX_API int hx_expert_gate_up_limited(const void* x, int ld_x, const void* gate_up, const int* chosen,
                              void* act, int dtype, int tokens, int top, int ff, int width,
-                             int experts, int activation, cudaStream_t stream) {
+                             int experts, int activation, float limit, cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && top > 0 && ff > 0 && width > 0 && experts > 0 && ld_x >= width,
              "hx_expert_gate_up: bad sizes");
   HX_REQUIRE(width * sizeof(float) <= 48 * 1024, "hx_expert_gate_up: rows of %d are too wide",
@@ -323,17 +383,24 @@ HX_API int hx_expert_gate_up(const void* x, int ld_x, const void* gate_up, const
   if (dtype == HX_F32) {
     hx_launch(expert_gate_up_kernel<float>, grid, EXPERT_WARPS * 32, shared, stream,
               static_cast<const float*>(x), ld_x, static_cast<const float*>(gate_up), chosen,
-              static_cast<float*>(act), top, ff, width, experts, activation);
+              static_cast<float*>(act), top, ff, width, experts, activation, limit);
   } else if (dtype == HX_BF16) {
     hx_launch(expert_gate_up_kernel<__nv_bfloat16>, grid, EXPERT_WARPS * 32, shared, stream,
               static_cast<const __nv_bfloat16*>(x), ld_x,
               static_cast<const __nv_bfloat16*>(gate_up), chosen, static_cast<__nv_bfloat16*>(act),
-              top, ff, width, experts, activation);
+              top, ff, width, experts, activation, limit);
   } else {
     HX_REQUIRE(false, "hx_expert_gate_up: unknown dtype %d", dtype);
   }
   HX_CHECK_LAUNCH("hx_expert_gate_up");
   return HX_OK;
+}
+
+HX_API int hx_expert_gate_up(const void* x, int ld_x, const void* gate_up, const int* chosen,
+                             void* act, int dtype, int tokens, int top, int ff, int width,
+                             int experts, int activation, cudaStream_t stream) {
+  return hx_expert_gate_up_limited(x, ld_x, gate_up, chosen, act, dtype, tokens, top, ff, width,
+                                   experts, activation, 0.0f, stream);
 }
 
 // act [tokens * top, ff] and down [experts, width, ff] in the compute dtype; out float32
@@ -419,5 +486,29 @@ HX_API int hx_expert_combine(const float* y, int ld_y, const int* pair_row, cons
   hx_launch(expert_combine_kernel, dim3((width + 511) / 512, tokens), 128, 0, stream, y, ld_y,
             pair_row, weights, out, ld_out, top, width);
   HX_CHECK_LAUNCH("hx_expert_combine");
+  return HX_OK;
+}
+
+// out float32 [tokens, ld_out] += x[token] * (sum of the weights of the token's choices with an
+// index >= experts): outputs of the router behind the experts return their input.
+HX_API int hx_expert_identity_add(const void* x, int ld_x, const int* chosen, const float* weights,
+                                  float* out, int ld_out, int dtype, int tokens, int top,
+                                  int width, int experts, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && top > 0 && width > 0 && ld_x >= width && ld_out >= width &&
+                 experts >= 0, "hx_expert_identity_add: bad sizes");
+  HX_REQUIRE(tokens <= 65535, "hx_expert_identity_add: at most 65535 tokens a step");
+  if (tokens == 0) return HX_OK;
+  const dim3 grid((width + 511) / 512, tokens);
+  if (dtype == HX_F32) {
+    hx_launch(expert_identity_kernel<float>, grid, 128, 0, stream, static_cast<const float*>(x),
+              ld_x, chosen, weights, out, ld_out, top, width, experts);
+  } else if (dtype == HX_BF16) {
+    hx_launch(expert_identity_kernel<__nv_bfloat16>, grid, 128, 0, stream,
+              static_cast<const __nv_bfloat16*>(x), ld_x, chosen, weights, out, ld_out, top, width,
+              experts);
+  } else {
+    HX_REQUIRE(false, "hx_expert_identity_add: unknown dtype %d", dtype);
+  }
+  HX_CHECK_LAUNCH("hx_expert_identity_add");
   return HX_OK;
 }

@@ -140,6 +140,10 @@ class DecoderModel:
         self.entry_parts = {index: build_part("entry", entry.before, spec.hidden_size)
                             for index, entry in enumerate(spec.schedule)
                             if entry.before is not None}
+        # and behind it
+        self.entry_parts_after = {index: build_part("entry", entry.after, spec.hidden_size)
+                                  for index, entry in enumerate(spec.schedule)
+                                  if entry.after is not None}
         self.final_norm: Norm = build_part("norm", spec.final_norm, spec.hidden_size)
         self.lm_head = build_part("lm_head", spec.lm_head, spec.hidden_size)
         self.dtype: Optional[torch.dtype] = None
@@ -154,6 +158,7 @@ class DecoderModel:
         for block in self.blocks:
             yield from block.parts()
         yield from self.entry_parts.values()
+        yield from self.entry_parts_after.values()
         yield self.final_norm
         yield self.lm_head
 
@@ -185,7 +190,8 @@ class DecoderModel:
         total = self.final_norm.weight_bytes() + self.lm_head.weight_bytes()
         for entry in self.schedule:
             total += sum(part.weight_bytes() for part in self.blocks[entry.block].parts())
-        total += sum(part.weight_bytes() for part in self.entry_parts.values())
+        total += sum(part.weight_bytes() for part in (*self.entry_parts.values(),
+                                                      *self.entry_parts_after.values()))
         return total
 
     # -------------------------------------------------------------------- cache
@@ -248,7 +254,10 @@ class DecoderModel:
             ops.streams_spread(first, residual, ctx.n_tokens, self.streams)
         else:
             self.embedding.forward(ctx, residual)
-        if any(entry.add_embedding for entry in self.schedule) or self.entry_parts:
+        # an entry part that does not read the embedding's output says so (needs_embedding)
+        if any(entry.add_embedding for entry in self.schedule) or any(
+                getattr(part, "needs_embedding", True)
+                for part in (*self.entry_parts.values(), *self.entry_parts_after.values())):
             if self.streams > 1:
                 raise ValueError("adding the embedding back in is defined for one residual stream")
             # the embedding's output is kept for the entries that add it back in
@@ -260,6 +269,8 @@ class DecoderModel:
             if index in self.entry_parts:
                 self.entry_parts[index].forward(ctx, residual, embedded)
             self.blocks[entry.block].forward(ctx, self.layer_cache(cache, index), residual, normed)
+            if index in self.entry_parts_after:
+                self.entry_parts_after[index].forward(ctx, residual, embedded)
             if self.after_entry is not None:
                 rows = residual[:ctx.n_tokens]
                 self.after_entry(index, rows if self.streams == 1 else

@@ -26,7 +26,10 @@ EPI_GEGLU_TANH = 5   # tensor-core kernel only: gelu_tanh(gate) * up
 
 GATE_SILU = 0        # what a gated feed-forward passes its gate through
 GATE_GELU_TANH = 1
-GATE_ACTIVATIONS = {"silu": GATE_SILU, "gelu_tanh": GATE_GELU_TANH}
+GATE_RELU = 2             # max(gate, 0) * up
+GATE_CLAMPED_SIGMOID = 3  # g = min(gate, L), u = clamp(up, -L, L): g * sigmoid(1.702 g) * (u + 1)
+GATE_ACTIVATIONS = {"silu": GATE_SILU, "gelu_tanh": GATE_GELU_TANH, "relu": GATE_RELU,
+                    "clamped_sigmoid": GATE_CLAMPED_SIGMOID}
 
 FLAG_BAD_TOKEN = 1
 FLAG_BAD_PAGE = 2
@@ -193,10 +196,44 @@ def _declare(library: ctypes.CDLL) -> None:
         getattr(library, name).restype = _c_int
     library.hx_latent_prepare.argtypes = [
         _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr,
-        _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+        _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+        _c_ptr]
     library.hx_latent_queries.argtypes = [
         _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
-        _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr]
+    library.hx_biased_gated_activation.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                                   _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr]
+    library.hx_route_top_ruled.argtypes = [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                                           _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_expert_gate_up_limited.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int,
+                                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                  _c_float, _c_ptr]
+    library.hx_expert_identity_add.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                               _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_gemm_tc_grouped_gated.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int,
+                                                 _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                                 _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr,
+                                                 _c_ptr]
+    library.hx_paged_attention_biased.argtypes = [
+        _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
+        _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+        _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_prefill_attention_biased.argtypes = [
+        *library.hx_prefill_attention_windowed.argtypes[:-2], _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_norm_residual_add.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_float, _c_float, _c_ptr,
+                                             _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_biased_normed_rows.argtypes = [
+        _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_float,
+        _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+        _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_head_gate.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_token_gate.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
+                                      _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
+    for name in ("hx_biased_gated_activation", "hx_route_top_ruled", "hx_expert_gate_up_limited",
+                 "hx_expert_identity_add", "hx_gemm_tc_grouped_gated", "hx_paged_attention_biased",
+                 "hx_prefill_attention_biased", "hx_norm_residual_add", "hx_biased_normed_rows",
+                 "hx_head_gate", "hx_token_gate"):
+        getattr(library, name).restype = _c_int
     library.hx_head_products.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
                                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
     for name in ("hx_linear_state_scan", "hx_gated_residual_add", "hx_join_rows", "hx_route_top",
@@ -348,16 +385,23 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
 
 
 def swiglu(gate_up: torch.Tensor, act: torch.Tensor, zero_input: bool = False,
-           activation: int = GATE_SILU) -> None:
-    """act[t, i] = f(gate_up[t, i]) * gate_up[t, I + i] with f = silu (or ``activation``:
-    GATE_GELU_TANH); gate_up float32, act compute dtype.
+           activation: int = GATE_SILU, gate_bias: Optional[torch.Tensor] = None,
+           up_bias: Optional[torch.Tensor] = None, limit: float = 0.0) -> None:
+    """act[t, i] = f(gate_up[t, i] + gate_bias[i]) * (gate_up[t, I + i] + up_bias[i]) with f =
+    silu (or ``activation``: any of GATE_ACTIVATIONS; the clamped form takes ``limit``);
+    gate_up and the optional biases float32, act compute dtype.
     ``zero_input`` clears what was read (gate_up is a split-K accumulator)."""
     tokens, intermediate = act.shape
     _need(gate_up, torch.float32, "gate_up")
     assert act.is_contiguous()
-    _check(lib().hx_gated_activation(gate_up.data_ptr(), act.data_ptr(), dtype_code(act.dtype),
-                                     tokens, intermediate, gate_up.stride(0),
-                                     1 if zero_input else 0, int(activation), _stream()))
+    for bias in (gate_bias, up_bias):
+        if bias is not None:
+            _need(bias, torch.float32, "bias")
+            assert bias.numel() == intermediate
+    _check(lib().hx_biased_gated_activation(
+        gate_up.data_ptr(), _ptr(gate_bias), _ptr(up_bias), act.data_ptr(), dtype_code(act.dtype),
+        tokens, intermediate, gate_up.stride(0), 1 if zero_input else 0, int(activation),
+        float(limit), _stream()))
 
 
 def short_conv_append(raw: Optional[torch.Tensor], accum: Optional[torch.Tensor],
@@ -544,27 +588,36 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     head_dim: int, page_size: int, num_pages: int, window: int, scale: float,
                     split_keys: int, max_splits: int, status: torch.Tensor,
                     request_start: Optional[torch.Tensor] = None, skip_query_len: int = 0,
-                    arrivals: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
+                    arrivals: Optional[torch.Tensor] = None, keep_first: int = 0,
+                    sinks: Optional[torch.Tensor] = None,
+                    slopes: Optional[torch.Tensor] = None) -> None:
     """out[t, h*D:(h+1)*D] = attention of query (t, h) over its request's pages.  With
     ``skip_query_len > 0`` tokens of requests that bring at least that many tokens are left
     out (the tensor-core kernel takes them).  With a window, keys at positions below
     ``keep_first`` stay visible behind it.  The call needs scratch, made here when it is
     not given: ``partial`` (float32, :func:`attention_scratch_floats` elements) and
     ``arrivals`` (int32, one counter per (token, head), zero on entry; the kernel leaves it
-    zero)."""
+    zero).  ``sinks`` (float32 ``[heads]``): the softmax's denominator also holds
+    ``exp(sinks[h])``, a term without key or value.  ``slopes`` (float32 ``[heads]``): the score
+    of key ``j`` for the query at position ``i`` is lowered by ``slopes[h] * (i - j)``."""
+    for per_head in (sinks, slopes):
+        if per_head is not None:
+            _need(per_head, torch.float32, "sinks and slopes")
+            assert per_head.numel() == heads
     if arrivals is None:
         arrivals = torch.zeros(max(1, tokens * heads), dtype=torch.int32, device=q.device)
     if partial is None:
         partial = torch.empty(attention_scratch_floats(tokens, heads, head_dim, max_splits,
                                                        q.dtype, page_size, window),
                               dtype=torch.float32, device=q.device)
-    _check(lib().hx_paged_attention_kept(
+    _check(lib().hx_paged_attention_biased(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q.dtype),
         positions.data_ptr(), token_request.data_ptr(), request_table_row.data_ptr(),
         block_tables.data_ptr(), block_tables.stride(0), _ptr(request_start), skip_query_len,
         out.data_ptr(), out.stride(0),
         _ptr(partial), _ptr(arrivals), tokens, heads, kv_heads, head_dim, page_size, num_pages, window,
-        int(keep_first), float(scale), split_keys, max_splits, _ptr(status), _stream()))
+        int(keep_first), float(scale), split_keys, max_splits, _ptr(sinks), _ptr(slopes),
+        _ptr(status), _stream()))
 
 
 PREFILL_TILE_ROWS = 64        # query rows of a CTA of the ``mma.sync`` prompt kernel
@@ -592,7 +645,9 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       min_query_len: int, status: torch.Tensor,
                       tensor_memory: Optional[bool] = None,
                       query_lengths: Optional[Sequence[int]] = None, window: int = 0,
-                      keep_first: int = 0, packed: bool = False) -> None:
+                      keep_first: int = 0, packed: bool = False,
+                      sinks: Optional[torch.Tensor] = None,
+                      slopes: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention (bfloat16) of every request that brings at least
     ``min_query_len`` tokens; ``tile_bound`` bounds the number of query tiles of 64 tokens
     (the tensor-memory kernel, whose tiles hold 256 tokens, needs no more).  A CTA that finds
@@ -605,7 +660,15 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     j < ``keep_first``; both kernels skip the tiles of keys that no row of a query tile sees.
     ``packed``: the ``mma.sync`` kernel with the heads of a key/value head side by side in a
     tile's rows (``prefill_attention_packed_tokens`` tokens a tile), which reads keys and
-    values once for all of them; it takes single decoded tokens as well."""
+    values once for all of them; it takes single decoded tokens as well.  ``sinks`` and
+    ``slopes`` as in :func:`paged_attention`; with either the ``mma.sync`` kernel runs."""
+    biased = sinks is not None or slopes is not None
+    for per_head in (sinks, slopes):
+        if per_head is not None:
+            _need(per_head, torch.float32, "sinks and slopes")
+            assert per_head.numel() == heads
+    if biased:
+        tensor_memory = False
     _need(q, torch.bfloat16, "q")
     _need(k_cache, torch.bfloat16, "k_cache")
     _need(out, torch.bfloat16, "out")
@@ -626,7 +689,11 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         request_context.data_ptr(), request_table_row.data_ptr(), block_tables.data_ptr(),
         block_tables.stride(0), out.data_ptr(), out.stride(0), requests, tile_bound, heads,
         kv_heads, head_dim, page_size, num_pages, float(scale), min_query_len)
-    if packed:
+    if biased:
+        _check(lib().hx_prefill_attention_biased(*arguments, int(window), int(keep_first),
+                                                 1 if packed else 0, _ptr(sinks), _ptr(slopes),
+                                                 _ptr(status), _stream()))
+    elif packed:
         _check(lib().hx_prefill_attention_packed(*arguments, int(window), int(keep_first),
                                                  _ptr(status), _stream()))
     elif tensor_memory:
@@ -952,34 +1019,129 @@ def join_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, tokens: int) 
                               dtype_code(out.dtype), tokens, width, _stream()))
 
 
+# ------------------------------------------------ norms between a product and what follows
+
+def norm_residual_add(residual: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                      mult: float, tokens: int, cast_out: Optional[torch.Tensor] = None) -> None:
+    """residual[:tokens] += mult * y / sqrt(mean(y^2) + eps) * weight (float32 rows); with
+    ``cast_out`` the updated rows are also written there in its dtype."""
+    _need(residual, torch.float32, "residual")
+    _need(y, torch.float32, "y")
+    _need(weight, torch.float32, "weight")
+    width = residual.shape[1]
+    assert residual.is_contiguous() and y.is_contiguous() and y.shape[1] == width
+    assert weight.numel() == width
+    code = dtype_code(cast_out.dtype) if cast_out is not None else HX_F32
+    _check(lib().hx_norm_residual_add(residual.data_ptr(), y.data_ptr(), weight.data_ptr(),
+                                      float(eps), float(mult), _ptr(cast_out),
+                                      cast_out.stride(0) if cast_out is not None else 0, code,
+                                      tokens, width, _stream()))
+
+
+def biased_normed_rows(projected: torch.Tensor, clear: bool, rows: torch.Tensor, tokens: int,
+                       heads: int, kv_heads: int, head_dim: int, value_dim: int, row_dim: int,
+                       positions: torch.Tensor, q_bias: Optional[torch.Tensor] = None,
+                       k_bias: Optional[torch.Tensor] = None,
+                       v_bias: Optional[torch.Tensor] = None,
+                       q_weight: Optional[torch.Tensor] = None,
+                       k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                       temp_coef: float = 0.0, temp_every: int = 0, value_mix: int = 0,
+                       mix: float = 0.0, value_source: Optional[torch.Tensor] = None,
+                       gates: Optional[torch.Tensor] = None) -> None:
+    """From the float32 projection ``[q | k | v | head gate sums]`` of every token: biases, one RMS
+    norm over all query coordinates and one over all key coordinates, the query times ``1 +
+    temp_coef * ln(floor((p + 1) / temp_every) + 1)``, values kept in (``value_mix`` 1) or
+    blended with (2: ``(1 - mix) v + mix * source``) ``value_source``; ``rows`` gets ``[heads |
+    kv_heads | kv_heads]`` rows of ``row_dim`` and ``gates`` ``[tokens, heads]`` the sigmoid of
+    the gate sums.  ``clear``: the projection is an accumulator and is left zero."""
+    _need(projected, torch.float32, "projected")
+    for vector in (q_bias, k_bias, v_bias, q_weight, k_weight, value_source, gates):
+        if vector is not None:
+            _need(vector, torch.float32, "a float32 argument")
+            assert vector.is_contiguous()
+    assert rows.stride(-1) == 1
+    _check(lib().hx_biased_normed_rows(
+        projected.data_ptr(), projected.stride(0), 1 if clear else 0, _ptr(q_bias), _ptr(k_bias),
+        _ptr(v_bias), _ptr(q_weight), _ptr(k_weight), float(eps), positions.data_ptr(),
+        float(temp_coef), int(temp_every), int(value_mix), float(mix), _ptr(value_source),
+        rows.data_ptr(), rows.stride(0), _ptr(gates), dtype_code(rows.dtype), tokens, heads,
+        kv_heads, head_dim, value_dim, row_dim, _stream()))
+
+
+def head_gate(context: torch.Tensor, gates: torch.Tensor, tokens: int, heads: int,
+              row_dim: int) -> None:
+    """context[t, h * row_dim:(h + 1) * row_dim] *= gates[t, h] (gates float32)."""
+    _need(gates, torch.float32, "gates")
+    assert gates.is_contiguous() and gates.shape[1] == heads and context.stride(-1) == 1
+    _check(lib().hx_head_gate(context.data_ptr(), context.stride(0), gates.data_ptr(),
+                              dtype_code(context.dtype), tokens, heads, row_dim, _stream()))
+
+
+def token_gate(sums: torch.Tensor, clear: bool, table: torch.Tensor, offset: int,
+               token_ids: torch.Tensor, out: torch.Tensor, tokens: int, dim: int,
+               status: Optional[torch.Tensor]) -> None:
+    """out[t, c] = gelu_tanh(sums[t, c]) * table[token_ids[t], offset + c] for ``c < dim``."""
+    _need(sums, torch.float32, "sums")
+    _need(token_ids, torch.int32, "token_ids")
+    assert table.dtype == out.dtype and table.stride(-1) == 1 and out.stride(-1) == 1
+    _check(lib().hx_token_gate(sums.data_ptr(), sums.stride(0), 1 if clear else 0,
+                               table.data_ptr(), table.stride(0), offset, table.shape[0],
+                               token_ids.data_ptr(), out.data_ptr(), out.stride(0),
+                               dtype_code(out.dtype), tokens, dim, _ptr(status), _stream()))
+
+
 # ------------------------------------------------------------------------ routed experts
 
 def route_top(sums: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, tokens: int,
-              experts: int, top: int, scale: float) -> None:
+              experts: int, top: int, scale: float, softmax: bool = False,
+              correction: Optional[torch.Tensor] = None, normalize: bool = True) -> None:
     """Per token the ``top`` largest of ``sigmoid(sums[:, :experts])`` (lowest index among
     equals) into ``chosen`` (int32 ``[tokens, top]``), and their scores over their sum
-    (``+ 1e-20``) times ``scale`` into ``weights`` (float32)."""
+    (``+ 1e-20``) times ``scale`` into ``weights`` (float32).  ``softmax``: the scores are
+    ``softmax(sums[:, :experts])``; ``correction`` (float32 ``[experts]``) is added to the scores
+    for the choice only; ``normalize=False``: the weights are the chosen scores times ``scale``."""
+    if correction is not None:
+        _need(correction, torch.float32, "correction")
+        assert correction.numel() == experts
     _need(sums, torch.float32, "sums")
     _need(chosen, torch.int32, "chosen")
     _need(weights, torch.float32, "weights")
     assert chosen.is_contiguous() and weights.is_contiguous()
     assert chosen.shape[1] == top and weights.shape[1] == top
-    _check(lib().hx_route_top(sums.data_ptr(), sums.stride(0), tokens, experts, top, float(scale),
-                              chosen.data_ptr(), weights.data_ptr(), _stream()))
+    _check(lib().hx_route_top_ruled(sums.data_ptr(), sums.stride(0), tokens, experts, top,
+                                    float(scale), 1 if softmax else 0, _ptr(correction),
+                                    1 if normalize else 0, chosen.data_ptr(), weights.data_ptr(),
+                                    _stream()))
 
 
 def expert_gate_up(x: torch.Tensor, gate_up: torch.Tensor, chosen: torch.Tensor,
-                   act: torch.Tensor, tokens: int, top: int, activation: int = GATE_SILU) -> None:
+                   act: torch.Tensor, tokens: int, top: int, activation: int = GATE_SILU,
+                   limit: float = 0.0) -> None:
     """act[t * top + k] = f(gate_e x[t]) * (up_e x[t]) with ``e = chosen[t, k]``; ``gate_up``
-    ``[experts, 2 * ff, width]`` holds an expert's gate rows, then its up rows."""
+    ``[experts, 2 * ff, width]`` holds an expert's gate rows, then its up rows.  A choice that
+    names no expert (``e >= experts``) is left out."""
     experts, rows, width = gate_up.shape
     ff = rows // 2
     assert x.dtype == gate_up.dtype == act.dtype and gate_up.is_contiguous()
     assert x.stride(-1) == 1 and x.shape[1] == width
     assert act.is_contiguous() and act.shape[1] == ff and act.shape[0] >= tokens * top
-    _check(lib().hx_expert_gate_up(x.data_ptr(), x.stride(0), gate_up.data_ptr(), chosen.data_ptr(),
-                                   act.data_ptr(), dtype_code(x.dtype), tokens, top, ff, width,
-                                   experts, int(activation), _stream()))
+    _check(lib().hx_expert_gate_up_limited(x.data_ptr(), x.stride(0), gate_up.data_ptr(),
+                                           chosen.data_ptr(), act.data_ptr(), dtype_code(x.dtype),
+                                           tokens, top, ff, width, experts, int(activation),
+                                           float(limit), _stream()))
+
+
+def expert_identity_add(x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
+                        out: torch.Tensor, tokens: int, top: int, experts: int) -> None:
+    """out[t] += x[t] * (the weights of the token's choices with an index ``>= experts``): the
+    router's outputs behind the experts return their input.  ``out`` float32."""
+    _need(out, torch.float32, "out")
+    width = x.shape[1]
+    assert x.stride(-1) == 1 and out.shape[1] >= width
+    _check(lib().hx_expert_identity_add(x.data_ptr(), x.stride(0), chosen.data_ptr(),
+                                        weights.data_ptr(), out.data_ptr(), out.stride(0),
+                                        dtype_code(x.dtype), tokens, top, width, experts,
+                                        _stream()))
 
 
 def expert_down(act: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor,
@@ -1047,14 +1209,24 @@ def expert_combine(y: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tenso
 
 def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, features: int,
                     epilogue: int, up_row_offset: int, token_tile: int, tile_group: torch.Tensor,
-                    status: torch.Tensor) -> None:
+                    status: torch.Tensor, gate_activation: Optional[int] = None,
+                    gate_limit: float = 0.0) -> None:
     """Tile ``t`` of ``token_tile`` rows of ``x`` times matrix ``tile_group[t]`` of ``w``
     ``[groups, group_rows, depth]`` on the tensor cores; ``rows`` bounds the rows in use (a
-    multiple of the tile).  Epilogues: plain store, float32 store, gated activation."""
+    multiple of the tile).  Epilogues: plain store, float32 store, gated activation; with
+    ``gate_activation`` (any of GATE_ACTIVATIONS, ``gate_limit`` for the clamped form) the
+    epilogue is that gated activation whatever ``epilogue`` says."""
     _need(x, torch.bfloat16, "x")
     _need(w, torch.bfloat16, "w")
     assert w.is_contiguous() and x.stride(-1) == 1 and out.stride(-1) == 1
     groups, group_rows, depth = w.shape
+    if gate_activation is not None:
+        _check(lib().hx_gemm_tc_grouped_gated(
+            x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), depth, group_rows, groups,
+            out.data_ptr(), out.stride(0), rows, features, depth, int(gate_activation),
+            float(gate_limit), up_row_offset, token_tile, tile_group.data_ptr(),
+            status.data_ptr(), _stream()))
+        return
     _check(lib().hx_gemm_tc_grouped(x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), depth,
                                     group_rows, groups, out.data_ptr(), out.stride(0), rows,
                                     features, depth, epilogue, up_row_offset, token_tile,
@@ -1067,7 +1239,8 @@ def latent_prepare(down: torch.Tensor, q_weight: torch.Tensor, kv_weight: torch.
                    positions: torch.Tensor, freq: Optional[torch.Tensor],
                    freq_exact: Optional[torch.Tensor], rotary_dims: int, layout: int,
                    query_latent: torch.Tensor, rows: torch.Tensor, key_offset: int, tokens: int,
-                   q_rank: int, kv_rank: int, rot: int, row_dim: int) -> None:
+                   q_rank: int, kv_rank: int, rot: int, row_dim: int,
+                   amplitude: float = 1.0) -> None:
     """From the float32 down-projection ``[q_rank | kv_rank | rot]`` of every token: the normed
     query latent into ``query_latent``; the key row ``[c | rot(kr) | 0]`` at column
     ``key_offset`` of ``rows`` and the value row ``[c | 0]`` behind it (``row_dim`` wide each),
@@ -1080,13 +1253,14 @@ def latent_prepare(down: torch.Tensor, q_weight: torch.Tensor, kv_weight: torch.
         down.data_ptr(), down.stride(0), q_weight.data_ptr(), kv_weight.data_ptr(), float(eps),
         positions.data_ptr(), _ptr(freq), _ptr(freq_exact), rotary_dims, layout,
         query_latent.data_ptr(), query_latent.stride(0), rows.data_ptr(), rows.stride(0),
-        key_offset, dtype_code(rows.dtype), tokens, q_rank, kv_rank, rot, row_dim, _stream()))
+        key_offset, dtype_code(rows.dtype), tokens, q_rank, kv_rank, rot, row_dim,
+        float(amplitude), _stream()))
 
 
 def latent_queries(q: torch.Tensor, rot_offset: int, rows: torch.Tensor, positions: torch.Tensor,
                    freq: Optional[torch.Tensor], freq_exact: Optional[torch.Tensor],
                    rotary_dims: int, layout: int, tokens: int, heads: int, kv_rank: int, rot: int,
-                   row_dim: int) -> None:
+                   row_dim: int, amplitude: float = 1.0) -> None:
     """The rotated part of every head's query (``q[:, rot_offset + head * rot:][:rot]``) turned
     by the token's position into ``rows[:, head * row_dim + kv_rank:]``, zeros to the head's
     end."""
@@ -1094,7 +1268,8 @@ def latent_queries(q: torch.Tensor, rot_offset: int, rows: torch.Tensor, positio
     _check(lib().hx_latent_queries(q.data_ptr(), q.stride(0), rot_offset, rows.data_ptr(),
                                    rows.stride(0), positions.data_ptr(), _ptr(freq),
                                    _ptr(freq_exact), rotary_dims, layout, dtype_code(rows.dtype),
-                                   tokens, heads, kv_rank, rot, row_dim, _stream()))
+                                   tokens, heads, kv_rank, rot, row_dim, float(amplitude),
+                                   _stream()))
 
 
 def head_products(x: torch.Tensor, x_stride: int, w: torch.Tensor, out: torch.Tensor,

@@ -26,6 +26,14 @@ Optional mechanisms, each a parameter (absent: as if it did not exist):
   ``sigmoid(g x)`` before the output projection (tensor ``g`` ``[heads*value_dim, hidden]``);
   with a filter the gate's projection is part of the fused product.
 
+* ``sinks`` (True): a learned number per head (tensor ``sink`` ``[heads]``) whose exponential
+  is one more term of the softmax's denominator; it has no key and no value.
+* ``distance_slopes`` (a number per head): the score of key ``j`` for the query at position
+  ``i`` is lowered by ``slope_h * (i - j)``.
+
+:class:`NormedProjectionAttention` adds what sits between the projection and the cache for
+models without a rotation; :class:`LatentAttention` caches one latent for all heads.
+
 At load the three projections are fused into one ``[(A + 2 Akv) D, H]`` matrix and,
 when the checkpoint rotates half-split pairs while the encoding rotates adjacent
 pairs, the rows of q and k are permuted per head to ``[0, D/2, 1, D/2+1, ...]``
@@ -82,6 +90,30 @@ def rotary_row_permutation(heads: int, head_dim: int, rotary_dim: int) -> torch.
     return torch.tensor(order, dtype=torch.long)
 
 
+def stretched_frequencies(dims: int, theta: float, scaling: Optional[Mapping[str, float]]):
+    """Frequencies of the ``dims / 2`` rotated pairs (float64 tensor) and the factor on sine and
+    cosine.  Without ``scaling``: ``f_i = theta^(-2i / dims)`` and 1.  With ``scaling``
+    (``factor``, ``original``: the trained length, ``fast`` and ``slow``: turns over that
+    length) a pair that turns more often than ``fast`` keeps its frequency, one that turns less
+    than ``slow`` takes ``f_i / factor``, and the pairs between are blended linearly in the
+    pair's index: with ``pair(t) = dims ln(original / (2 pi t)) / (2 ln theta)``, ``lo =
+    max(floor(pair(fast)), 0)``, ``hi = min(ceil(pair(slow)), dims - 1)`` and ``r_i =
+    clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` the frequency is ``f_i / factor * r_i + f_i
+    (1 - r_i)``; sine and cosine are multiplied by ``0.1 ln(factor) + 1``."""
+    index = torch.arange(dims // 2, dtype=torch.float64)
+    plain = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * index / float(dims))
+    if not scaling:
+        return plain, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def pair_of(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+    lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair_of(float(scaling["slow"]))), dims - 1)
+    ramp = torch.clamp((index - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return plain / factor * ramp + plain * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
 class PagedAttention(Mixer):
     pack_heads = False      # subclasses whose heads share few cached rows set this
 
@@ -104,6 +136,7 @@ class PagedAttention(Mixer):
         if gate not in (None, "sigmoid"):
             raise ValueError(f"output gate {gate!r} has no kernel; only 'sigmoid'")
         self.gated = gate is not None
+        self._init_score_terms(spec)
         self.row_dim = self.head_dim
         self.position = build_part("position", spec["position"], hidden_size)
         wide = row_width(max(self.head_dim, self.value_dim))
@@ -141,6 +174,29 @@ class PagedAttention(Mixer):
         self.w_g: Optional[Weight] = None
         self.conv_filter: Optional[torch.Tensor] = None
 
+    def _init_score_terms(self, spec: PartSpec) -> None:
+        """The optional per-head terms of the scores: sinks and distance slopes."""
+        self.has_sinks = bool(spec.get("sinks", False))
+        slopes = spec.get("distance_slopes")
+        if slopes is not None and len(slopes) != self.heads:
+            raise ValueError("distance_slopes gives one slope per head")
+        self.slope_values = None if slopes is None else tuple(float(v) for v in slopes)
+        self.sinks: Optional[torch.Tensor] = None
+        self.slopes: Optional[torch.Tensor] = None
+
+    def _score_term_requests(self) -> List[TensorRequest]:
+        if not self.has_sinks:
+            return []
+        return [TensorRequest(self.names["sink"], (self.heads,), role="scale")]
+
+    def _bind_score_terms(self, tensors: Mapping[str, torch.Tensor], device) -> None:
+        if self.has_sinks:
+            self.sinks = tensors[self.names["sink"]].to(device=device, dtype=torch.float32) \
+                .contiguous()
+        if self.slope_values is not None:
+            self.slopes = torch.tensor(self.slope_values, dtype=torch.float64) \
+                .to(torch.float32).to(device).contiguous()
+
     def kv_need(self) -> Optional[KvNeed]:
         return KvNeed(self.kv_heads, self.row_dim, self.window, self.keep_first)
 
@@ -157,6 +213,7 @@ class PagedAttention(Mixer):
             TensorRequest(self.names["v"], (self.v_rows, h)),
             TensorRequest(self.names["o"], (h, self.o_columns)),
             *self.position.tensor_requests(),
+            *self._score_term_requests(),
         ]
         if self.gated:
             requests.append(TensorRequest(self.names["g"], (self.o_columns, h)))
@@ -217,6 +274,7 @@ class PagedAttention(Mixer):
             ], dim=0).to(device=device, dtype=torch.float32).contiguous()
         self.dtype = dtype
         self.position.bind(tensors, dtype, device)
+        self._bind_score_terms(tensors, device)
 
     @property
     def graph_safe(self) -> bool:
@@ -292,7 +350,8 @@ class PagedAttention(Mixer):
                                   context, ctx.n_requests, n, self.heads, self.kv_heads,
                                   self.row_dim, cache.page_size, cache.num_pages, self.scale, 1,
                                   ctx.status, query_lengths=ctx.host_query_lengths,
-                                  window=window, keep_first=kept, packed=True)
+                                  window=window, keep_first=kept, packed=True,
+                                  sinks=self.sinks, slopes=self.slopes)
             return
         if tensor_cores:
             ops.prefill_attention(qkv, cache.keys, cache.values, ctx.request_start,
@@ -301,7 +360,7 @@ class PagedAttention(Mixer):
                                   self.kv_heads, self.row_dim, cache.page_size, cache.num_pages,
                                   self.scale, TENSOR_CORE_MIN_QUERY, ctx.status,
                                   query_lengths=ctx.host_query_lengths, window=window,
-                                  keep_first=kept)
+                                  keep_first=kept, sinks=self.sinks, slopes=self.slopes)
         if not tensor_cores or ctx.min_query_len < TENSOR_CORE_MIN_QUERY:
             longest = ctx.max_context_len if not window else \
                 min(ctx.max_context_len, window + kept)
@@ -318,7 +377,8 @@ class PagedAttention(Mixer):
                                 cache.num_pages, window, self.scale, split_keys, max_splits,
                                 ctx.status, request_start=ctx.request_start,
                                 skip_query_len=TENSOR_CORE_MIN_QUERY if tensor_cores else 0,
-                                arrivals=arrivals, keep_first=kept)
+                                arrivals=arrivals, keep_first=kept, sinks=self.sinks,
+                                slopes=self.slopes)
 
     def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
                 residual: torch.Tensor) -> None:
@@ -362,6 +422,154 @@ class PagedAttention(Mixer):
         project(context, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
 
 
+class NormedProjectionAttention(PagedAttention):
+    """Attention without a rotation whose projection is worked on as a whole before it is cached.
+
+    On top of :class:`PagedAttention`'s ``num_heads``, ``num_kv_heads``, ``head_dim``,
+    ``value_dim``, ``scale``, ``window``, ``sinks`` and ``distance_slopes`` (the position encoding
+    is ``none``), each optional:
+
+    * ``bias`` (True): q, k and v have biases (tensors ``q_bias``, ``k_bias``, ``v_bias``), added
+      to the projection's float32 sums;
+    * ``whole_norm`` (``{"eps": ...}``): ONE RMS norm over all of a token's query coordinates and
+      one over all of its key coordinates, before they are cut into heads (plain weights
+      ``q_norm`` ``[heads * head_dim]`` and ``k_norm`` ``[kv_heads * head_dim]``);
+    * ``query_temperature`` (``{"coef": c, "every": n}``): the query at position ``p`` is
+      multiplied by ``1 + c ln(floor((p + 1) / n) + 1)``;
+    * ``value_mix`` (``"source"`` or ``"mix"``): the first such layer of a model keeps its
+      values of the step's tokens (``"source"``), every later one caches and uses ``(1 - l) v +
+      l v_source`` with ``l`` the scalar tensor ``value_mix``; the layers agree in ``num_kv_heads *
+      value_dim``;
+    * ``output_gate`` ``"sigmoid_per_head"``: head ``h`` of the result is multiplied by
+      ``sigmoid(G x)_h``, ONE number per head (tensor ``g`` ``[heads, hidden]``).
+
+    ``[q | k | v | g]`` is one product with float32 sums (a weight stream for few tokens); one
+    kernel then adds the biases, norms, scales, blends, takes the gates' sigmoid and writes
+    queries, keys and values in rows of ``row_dim``; the plain append, the paged attention with
+    its sinks and slopes, the gate and the output matrix follow.
+    """
+
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        gate = spec.get("output_gate")
+        if gate not in (None, "sigmoid_per_head"):
+            raise ValueError(f"output gate {gate!r}: this part has 'sigmoid_per_head' only")
+        inner = {key: value for key, value in spec.params.items() if key != "output_gate"}
+        inner["position"] = PartSpec("none", {"head_dim": int(spec["head_dim"])})
+        super().__init__(PartSpec(spec.kind, inner, spec.tensors), hidden_size)
+        if self.conv_taps > 1:
+            raise ValueError("this part has no filter over time")
+        self.spec = spec
+        self.head_gated = gate is not None
+        self.bias = bool(spec.get("bias", False))
+        norm = spec.get("whole_norm")
+        self.whole_norm = norm is not None
+        self.eps = float(norm["eps"]) if norm else 0.0
+        if self.whole_norm and not self.eps > 0.0:
+            raise ValueError("the norm over the projection needs a positive eps")
+        temperature = spec.get("query_temperature")
+        self.temp_coef = float(temperature["coef"]) if temperature else 0.0
+        self.temp_every = int(temperature["every"]) if temperature else 0
+        if temperature and self.temp_every < 1:
+            raise ValueError("query_temperature.every counts positions: at least 1")
+        mix = spec.get("value_mix")
+        if mix not in (None, "source", "mix"):
+            raise ValueError(f"value_mix {mix!r} is neither 'source' nor 'mix'")
+        self.value_mix = {None: 0, "source": 1, "mix": 2}[mix]
+        self.mix = 0.0
+        # the projection's columns as the checkpoint has them: no padding inside a head
+        self.projected_size = self.q_rows + self.kv_rows + self.v_rows + \
+            (self.heads if self.head_gated else 0)
+        self.w_proj: Optional[Weight] = None
+        self.q_bias = self.k_bias = self.v_bias = None
+        self.q_norm = self.k_norm = None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        h = self.hidden_size
+        requests = [
+            TensorRequest(self.names["q"], (self.q_rows, h)),
+            TensorRequest(self.names["k"], (self.kv_rows, h)),
+            TensorRequest(self.names["v"], (self.v_rows, h)),
+            TensorRequest(self.names["o"], (h, self.o_columns)),
+            *self._score_term_requests(),
+        ]
+        if self.bias:
+            requests += [TensorRequest(self.names["q_bias"], (self.q_rows,), role="scale"),
+                         TensorRequest(self.names["k_bias"], (self.kv_rows,), role="scale"),
+                         TensorRequest(self.names["v_bias"], (self.v_rows,), role="scale")]
+        if self.whole_norm:
+            requests += [TensorRequest(self.names["q_norm"], (self.q_rows,), role="scale"),
+                         TensorRequest(self.names["k_norm"], (self.kv_rows,), role="scale")]
+        if "value_mix" in self.names:
+            # the blend of a layer that only keeps its values (or does not mix at all) may be in
+            # the checkpoint too, unused
+            requests.append(TensorRequest(self.names["value_mix"], (), role="scale",
+                                          optional=self.value_mix != 2))
+        if self.head_gated:
+            requests.append(TensorRequest(self.names["g"], (self.heads, h)))
+        return requests
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        def vector(role: str) -> torch.Tensor:
+            return tensors[self.names[role]].to(device=device, dtype=torch.float32).contiguous()
+        fused = [tensors[self.names[name]] for name in ("q", "k", "v")]
+        if self.head_gated:
+            fused.append(tensors[self.names["g"]])
+        self.w_proj = Weight(torch.cat(fused, dim=0).to(device=device, dtype=dtype).contiguous())
+        o = self.widen_rows(tensors[self.names["o"]].t().contiguous(), self.heads,
+                            self.value_dim).t()
+        self.w_o = Weight(o.to(device=device, dtype=dtype).contiguous())
+        if self.bias:
+            self.q_bias, self.k_bias, self.v_bias = (vector("q_bias"), vector("k_bias"),
+                                                     vector("v_bias"))
+        if self.whole_norm:
+            self.q_norm, self.k_norm = vector("q_norm"), vector("k_norm")
+        if self.value_mix == 2:
+            self.mix = float(tensors[self.names["value_mix"]].to(torch.float64).cpu())
+        self.dtype = dtype
+        self.position.bind(tensors, dtype, device)
+        self._bind_score_terms(tensors, device)
+
+    def weight_bytes(self) -> int:
+        return self.w_proj.nbytes() + self.w_o.nbytes()
+
+    def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
+                residual: torch.Tensor) -> None:
+        n = ctx.n_tokens
+        get = ctx.workspace.get
+        qkv = get(f"attention.qkv/{self.qkv_size}", (ctx.capacity, self.qkv_size), ctx.dtype)
+        context = get(f"attention.context/{self.q_size}", (ctx.capacity, self.q_size), ctx.dtype)
+        gates = get(f"attention.head_gates/{self.heads}", (ctx.capacity, self.heads),
+                    torch.float32) if self.head_gated else None
+        # every value-mixing layer of a model reads and writes the same buffer: the first one's
+        # values of this step's tokens
+        source = get(f"attention.value_source/{self.v_rows}", (ctx.capacity, self.v_rows),
+                     torch.float32) if self.value_mix else None
+        if is_weight_stream(x, self.w_proj, n):
+            projected = ctx.workspace.accumulator(f"attention.projected/{self.projected_size}",
+                                                  (STREAMING_MAX_TOKENS, self.projected_size))
+            project_into_accumulator(x, self.w_proj, projected, n, ctx.status, ctx.ordered_sums)
+            clear = True
+        else:
+            projected = get(f"attention.projected_sums/{self.projected_size}",
+                            (ctx.capacity, self.projected_size), torch.float32)
+            project(x, self.w_proj, projected, n, ops.EPI_STORE_F32, ctx.status)
+            clear = False
+        ops.biased_normed_rows(projected, clear, qkv, n, self.heads, self.kv_heads, self.head_dim,
+                               self.value_dim, self.row_dim, ctx.positions, q_bias=self.q_bias,
+                               k_bias=self.k_bias, v_bias=self.v_bias, q_weight=self.q_norm,
+                               k_weight=self.k_norm, eps=self.eps, temp_coef=self.temp_coef,
+                               temp_every=self.temp_every, value_mix=self.value_mix, mix=self.mix,
+                               value_source=source, gates=gates)
+        self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)      # the plain append
+        self.attend(ctx, cache, qkv, context)
+        if self.head_gated:
+            ops.head_gate(context, gates, n, self.heads, self.row_dim)
+        project(context, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
+
+
 class LatentAttention(PagedAttention):
     """Attention whose keys and values of all heads are functions of one small latent per
     token, which is all that is cached.
@@ -371,8 +579,9 @@ class LatentAttention(PagedAttention):
     all heads), ``value_dim``, ``kv_rank`` (the cached latent), ``q_rank`` (the queries' own
     latent), ``scale``, ``window`` (None: all earlier keys), ``eps`` (of both latents' RMS
     norms, which have plain weights), ``rotary`` (``theta``, ``dims``: the leading rotated
-    coordinates that are turned; ``layout`` ``interleaved`` or ``halves``), ``output_gate``
-    (``"sigmoid"`` or None).  Tensors: ``q_down`` ``[q_rank, hidden]``, ``q_norm``
+    coordinates that are turned; ``layout`` ``interleaved`` or ``halves``; ``scaling``: see
+    :func:`stretched_frequencies`), ``output_gate`` (``"sigmoid"`` or None), ``sinks`` (True:
+    tensor ``sink`` ``[heads]``, a term of every head's softmax denominator).  Tensors: ``q_down`` ``[q_rank, hidden]``, ``q_norm``
     ``[q_rank]``, ``q_up`` ``[heads * (head_dim + rotated_dim), q_rank]`` (per head the
     unrotated rows, then the rotated ones), ``kv_down`` ``[kv_rank + rotated_dim, hidden]``,
     ``kv_norm`` ``[kv_rank]``, ``k_up`` ``[heads * head_dim, kv_rank]``, ``v_up``
@@ -413,10 +622,15 @@ class LatentAttention(PagedAttention):
             raise ValueError(f"unknown rotary layout {layout!r}")
         self.rotary_layout = ops.ROTARY_LAYOUTS[layout]
         self.theta = float(rotary.get("theta", 10000.0))
+        self.rotary_scaling = rotary.get("scaling")
+        self.amplitude = 1.0
         gate = spec.get("output_gate")
         if gate not in (None, "sigmoid"):
             raise ValueError(f"output gate {gate!r} has no kernel; only 'sigmoid'")
         self.gated = gate is not None
+        self._init_score_terms(spec)
+        if self.slope_values is not None:
+            raise ValueError("latent attention takes no distance slopes")
         self.head_dim = self.kv_rank + self.rotated_dim        # of the one cached key head
         self.row_dim = row_width(self.head_dim)
         self.row_dim += self.row_dim % 2                       # the append moves pairs
@@ -449,6 +663,7 @@ class LatentAttention(PagedAttention):
             TensorRequest(self.names["k_up"], (self.heads * self.plain_dim, self.kv_rank)),
             TensorRequest(self.names["v_up"], (self.o_columns, self.kv_rank)),
             TensorRequest(self.names["o"], (h, self.o_columns)),
+            *self._score_term_requests(),
         ]
         if self.gated:
             requests.append(TensorRequest(self.names["g"], (self.o_columns, h)))
@@ -477,12 +692,12 @@ class LatentAttention(PagedAttention):
         self.q_norm, self.kv_norm = scale("q_norm"), scale("kv_norm")
         self.freq = self.freq_exact = None
         if self.rotary_dims:
-            exponent = -2.0 * torch.arange(self.rotary_dims // 2, dtype=torch.float64) \
-                / float(self.rotary_dims)
-            exact = torch.pow(torch.tensor(self.theta, dtype=torch.float64), exponent)
+            exact, self.amplitude = stretched_frequencies(self.rotary_dims, self.theta,
+                                                          self.rotary_scaling)
             self.freq_exact = exact.to(device).contiguous()
             self.freq = exact.to(torch.float32).to(device).contiguous()
         self._no_angles = torch.zeros((1, 1), dtype=torch.float32, device=device)
+        self._bind_score_terms(tensors, device)
         self.dtype = dtype
 
     def weight_bytes(self) -> int:
@@ -504,13 +719,14 @@ class LatentAttention(PagedAttention):
         ops.latent_prepare(down, self.q_norm, self.kv_norm, self.eps, ctx.positions, self.freq,
                            self.freq_exact, self.rotary_dims, self.rotary_layout, latent, rows,
                            self.q_size, n, self.q_rank, self.kv_rank, self.rotated_dim,
-                           self.row_dim)
+                           self.row_dim, amplitude=self.amplitude)
         project(latent, self.w_q_up, q, n, ops.EPI_STORE, ctx.status)
         # [Uk_h' q_h | rot(qr_h) | 0] per head
         ops.head_products(q, self.plain_dim, self.w_k_up, rows, self.row_dim, n)
         ops.latent_queries(q, self.heads * self.plain_dim, rows, ctx.positions, self.freq,
                            self.freq_exact, self.rotary_dims, self.rotary_layout, n, self.heads,
-                           self.kv_rank, self.rotated_dim, self.row_dim)
+                           self.kv_rank, self.rotated_dim, self.row_dim,
+                           amplitude=self.amplitude)
         write = cache.owns and cache.keys is not None
         ops.rope_append(rows, ctx.positions, ctx.token_request, ctx.request_slot,
                         cache.block_tables, cache.keys if write else None,
@@ -528,3 +744,4 @@ class LatentAttention(PagedAttention):
 
 register_part("mixer", "paged_attention", PagedAttention)
 register_part("mixer", "latent_attention", LatentAttention)
+register_part("mixer", "normed_projection_attention", NormedProjectionAttention)

@@ -155,3 +155,27 @@ def project_swiglu(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: t
                                 torch.float32)
         _gemm_simt(x, w_gate_up, scratch, tokens, ops.EPI_STORE_F32)
         ops.swiglu(scratch[:tokens], act[:tokens], activation=activation)
+
+
+def project_gated(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: torch.Tensor,
+                  workspace, capacity: int, tokens: int, status: torch.Tensor,
+                  ordered: bool, activation: int, gate_bias: Optional[torch.Tensor] = None,
+                  up_bias: Optional[torch.Tensor] = None, limit: float = 0.0) -> None:
+    """``act[:tokens] = f(x @ gate.T + gate_bias, x @ up.T + up_bias)`` for any of
+    ``ops.GATE_ACTIVATIONS``, biases optional: the product leaves float32 sums (a split-K weight
+    stream for few tokens, else the tensor-core or CUDA-core product with a float32 store) and
+    one kernel adds the biases, applies the gate and rounds once."""
+    if tokens == 0:
+        return
+    if is_weight_stream(x, w_gate_up, tokens):
+        sums = workspace.accumulator(f"mlp.gate_up/{intermediate}",
+                                     (STREAMING_MAX_TOKENS, 2 * intermediate))
+        project_into_accumulator(x, w_gate_up, sums, tokens, status, ordered)
+        clear = True
+    else:
+        sums = workspace.get(f"mlp.gate_up/{intermediate}", (capacity, 2 * intermediate),
+                             torch.float32)
+        project(x, w_gate_up, sums, tokens, ops.EPI_STORE_F32, status)
+        clear = False
+    ops.swiglu(sums[:tokens], act[:tokens], zero_input=clear, activation=activation,
+               gate_bias=gate_bias, up_bias=up_bias, limit=limit)

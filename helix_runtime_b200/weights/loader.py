@@ -55,6 +55,7 @@ class TensorRequest:
     shape: Tuple[int, ...]
     role: str = "matmul"            # matmul | embedding | scale | table
     fallback: Optional[str] = None  # another tensor that may stand in (tied weights)
+    optional: bool = False          # a checkpoint may hold it or not; absent, it is not loaded
 
 
 _FLOAT_STORAGE = {"F32", "F16", "BF16"}
@@ -85,7 +86,8 @@ def check_checkpoint(checkpoint: Checkpoint, requests: Iterable[TensorRequest]) 
             if request.fallback is not None and request.fallback in available:
                 source = request.fallback
             else:
-                missing.append(request.name)
+                if not request.optional:
+                    missing.append(request.name)
                 continue
         used.add(source)
         record = checkpoint.record(source)
@@ -109,6 +111,8 @@ def load_tensors(checkpoint: Checkpoint, requests: Sequence[TensorRequest],
     result: Dict[str, torch.Tensor] = {}
     nonfinite: List[str] = []
     for request in requests:
+        if request.name not in sources:       # an optional tensor the checkpoint does not hold
+            continue
         tensor = checkpoint.read(sources[request.name])
         if tensor.is_floating_point() and not bool(torch.isfinite(tensor.float()).all()):
             nonfinite.append(f"non-finite values in {sources[request.name]}")

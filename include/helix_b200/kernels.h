@@ -87,6 +87,12 @@ int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int intermed
    a = 0.044715 */
 int hx_gated_activation(float* gate_up, void* act, int out_dtype, int tokens, int intermediate,
                         int ld_in, int zero_input, int activation, cudaStream_t stream);
+/* the same with biases on gate and up (either may be null) and two more activations: 2: g =
+   relu; 3: the clamped form with its limit L, min(gate, L) * sigmoid(1.702 min(gate, L)) *
+   (clamp(up, -L, L) + 1) */
+int hx_biased_gated_activation(float* gate_up, const float* gate_bias, const float* up_bias,
+                               void* act, int out_dtype, int tokens, int intermediate, int ld_in,
+                               int zero_input, int activation, float limit, cudaStream_t stream);
 /* context[t, :width] *= sigmoid(gate[t, :width]); clear (may be null): float32 rows
    [tokens, clear_width] that are zeroed afterwards */
 int hx_sigmoid_gate(void* context, int ld_context, const void* gate, int ld_gate, int dtype,
@@ -200,16 +206,53 @@ int hx_gated_residual_add(float* residual, const float* output, const float* gat
 int hx_join_rows(const float* a, const float* b, void* out, int ld_out, int dtype, int tokens,
                  int width, cudaStream_t stream);
 
+/* ---- norms between a product and what follows it ---------------------------------------- */
+/* residual[t] += mult * y[t] / sqrt(mean(y[t]^2) + eps) * weight (float32 [tokens][width]);
+ * cast_out (may be null): the updated rows in `dtype` */
+int hx_norm_residual_add(float* residual, const float* y, const float* weight, float eps,
+                         float mult, void* cast_out, int ld_cast, int dtype, int tokens, int width,
+                         cudaStream_t stream);
+/* projected float32 = [heads * head_dim q | kv_heads * head_dim k | kv_heads * value_dim v |
+ * heads gate sums (with gates)]: biases (may be null), one RMS norm over ALL of a token's q
+ * and one over all of its k (weights null: none), q times 1 + temp_coef * ln(floor((p + 1) /
+ * temp_every) + 1) (temp_every 0: none), value_mix 1: v is stored in value_source, 2: v <- (1 -
+ * lambda) v + lambda value_source; rows = [heads | kv_heads | kv_heads] rows of row_dim in
+ * `dtype`; gates (may be null) [tokens][heads] = sigmoid of the gate sums; clear: projected is
+ * left zero */
+int hx_biased_normed_rows(float* projected, int ld_projected, int clear, const float* q_bias,
+                          const float* k_bias, const float* v_bias, const float* q_weight,
+                          const float* k_weight, float eps, const int* positions, float temp_coef,
+                          int temp_every, int value_mix, float lambda, float* value_source,
+                          void* rows, int ld_rows, float* gates, int dtype, int tokens, int heads,
+                          int kv_heads, int head_dim, int value_dim, int row_dim,
+                          cudaStream_t stream);
+/* context[t][h * row_dim + c] *= gates[t][h] */
+int hx_head_gate(void* context, int ld_context, const float* gates, int dtype, int tokens,
+                 int heads, int row_dim, cudaStream_t stream);
+/* out[t][c] = gelu_tanh(sums[t][c]) * table[token_ids[t]][offset + c], c < dim */
+int hx_token_gate(float* sums, int ld_sums, int clear, const void* table, int ld_table, int offset,
+                  int vocab, const int* token_ids, void* out, int ld_out, int dtype, int tokens,
+                  int dim, int* status, cudaStream_t stream);
+
 /* ---- routed experts --------------------------------------------------------------------- */
 /* s = sigmoid(sums); the `top` largest (lowest index among equals); weights s / (sum of the
  * chosen + 1e-20) * scale; chosen and weights [tokens][top] */
 int hx_route_top(const float* sums, int ld, int tokens, int experts, int top, float scale,
                  int* chosen, float* weights, cudaStream_t stream);
+/* the same by a rule: softmax != 0: s = softmax(sums) over all `experts` outputs; correction
+ * [experts] (may be null) is added to s for the choice only; normalize 0: weights s * scale */
+int hx_route_top_ruled(const float* sums, int ld, int tokens, int experts, int top, float scale,
+                       int softmax, const float* correction, int normalize, int* chosen,
+                       float* weights, cudaStream_t stream);
 /* act[t * top + k] = f(Wg[e] x[t]) * (Wu[e] x[t]), e = chosen[t][k]; gate_up [experts][2 ff]
  * [width] (gate rows first) */
 int hx_expert_gate_up(const void* x, int ld_x, const void* gate_up, const int* chosen, void* act,
                       int dtype, int tokens, int top, int ff, int width, int experts,
                       int activation, cudaStream_t stream);
+/* the same for every gate activation of hx_biased_gated_activation, with the clamped form's limit */
+int hx_expert_gate_up_limited(const void* x, int ld_x, const void* gate_up, const int* chosen,
+                              void* act, int dtype, int tokens, int top, int ff, int width,
+                              int experts, int activation, float limit, cudaStream_t stream);
 /* out[t] += sum_k weights[t][k] * Wd[chosen[t][k]] act[t * top + k], k ascending; out float32 */
 int hx_expert_down(const void* act, const void* down, const int* chosen, const float* weights,
                    float* out, int ld_out, int dtype, int tokens, int top, int ff, int width,
@@ -228,6 +271,11 @@ int hx_expert_gather(const void* x, int ld_x, const int* pair_row, void* grouped
 int hx_expert_combine(const float* y, int ld_y, const int* pair_row, const float* weights,
                       float* out, int ld_out, int tokens, int top, int width,
                       cudaStream_t stream);
+/* out[t] += x[t] * (sum of weights[t][k] over the choices with chosen[t][k] >= experts): router
+ * outputs behind the experts return their input */
+int hx_expert_identity_add(const void* x, int ld_x, const int* chosen, const float* weights,
+                           float* out, int ld_out, int dtype, int tokens, int top, int width,
+                           int experts, cudaStream_t stream);
 
 /* ---- attention over a cached latent ----------------------------------------------------- */
 /* down [tokens][q_rank + kv_rank + rot] float32: both latents RMS-normed with a weight; the
@@ -237,14 +285,15 @@ int hx_latent_prepare(const float* down, int ld_down, const float* q_weight,
                       const float* kv_weight, float eps, const int* positions, const float* freq,
                       const double* freq_exact, int rotary_dims, int layout, void* query_latent,
                       int ld_latent, void* rows, int ld_rows, int key_offset, int dtype,
-                      int tokens, int q_rank, int kv_rank, int rot, int row_dim,
+                      int tokens, int q_rank, int kv_rank, int rot, int row_dim, float amplitude,
                       cudaStream_t stream);
+/* (amplitude: a factor on sine and cosine, 1 unless the frequencies are stretched) */
 /* every head's rotated query part (q at rot_offset inside a head), turned by the position,
  * behind the head's kv_rank latent coordinates in `rows`, zeros to row_dim */
 int hx_latent_queries(const void* q, int ld_q, int rot_offset, void* rows, int ld_rows,
                       const int* positions, const float* freq, const double* freq_exact,
                       int rotary_dims, int layout, int dtype, int tokens, int heads, int kv_rank,
-                      int rot, int row_dim, cudaStream_t stream);
+                      int rot, int row_dim, float amplitude, cudaStream_t stream);
 /* out[t][h * out_stride + o] = sum_i w[h][o][i] * x[t][h * x_stride + i] */
 int hx_head_products(const void* x, int ld_x, int x_stride, const void* w, void* out, int ld_out,
                      int out_stride, int dtype, int tokens, int heads, int out_dim, int in_dim,
@@ -313,6 +362,13 @@ int hx_gemm_tc_grouped(const void* x, int ldx, int x_capacity_rows, const void* 
                        int group_rows, int groups, void* out, int ldo, int tokens, int features,
                        int depth, int epilogue, int up_row_offset, int token_tile,
                        const int* tile_group, int* status, cudaStream_t stream);
+/* the grouped product with the gated epilogue for every gate activation (see
+ * hx_biased_gated_activation); gate_limit: the clamped form's limit */
+int hx_gemm_tc_grouped_gated(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                             int group_rows, int groups, void* out, int ldo, int tokens,
+                             int features, int depth, int activation, float gate_limit,
+                             int up_row_offset, int token_tile, const int* tile_group,
+                             int* status, cudaStream_t stream);
 
 /* ---- attention over the paged cache ----------------------------------------------------- */
 int hx_cache_chunk_elements(int dtype, int head_dim);
@@ -338,6 +394,18 @@ int hx_paged_attention_kept(const void* q, int ldq, const void* k_cache, const v
                             int heads, int kv_heads, int head_dim, int page_size, int num_pages,
                             int window, int keep_first, float scale, int split_keys,
                             int max_splits, int* status, cudaStream_t stream);
+/* the same with two optional float32 arrays per query head (null: absent): sinks: the softmax's
+   denominator also holds exp(sinks[h]), a term without key or value; slopes: the score of key j
+   for the query at position i is lowered by slopes[h] * (i - j) */
+int hx_paged_attention_biased(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                              int dtype, const int* positions, const int* token_request,
+                              const int* request_table_row, const int* block_tables,
+                              int table_stride, const int* request_start, int skip_query_len,
+                              void* out, int ldo, float* partial, int* arrivals, int tokens,
+                              int heads, int kv_heads, int head_dim, int page_size, int num_pages,
+                              int window, int keep_first, float scale, int split_keys,
+                              int max_splits, const float* sinks, const float* slopes,
+                              int* status, cudaStream_t stream);
 /* the same with scratch built into the library: see hx_no_alloc.h beside the sources */
 int hx_paged_attention_no_alloc(const void* q, int ldq, const void* k_cache, const void* v_cache,
                                 int dtype, const int* positions, const int* token_request,
@@ -376,6 +444,16 @@ int hx_prefill_attention_packed(const void* q, int ldq, const void* k_cache, con
                                 int tile_bound, int heads, int kv_heads, int head_dim,
                                 int page_size, int num_pages, float scale, int min_query_len,
                                 int window, int keep_first, int* status, cudaStream_t stream);
+/* hx_prefill_attention_windowed (pack_heads 0) or hx_prefill_attention_packed (pack_heads != 0)
+ * with the optional sinks and slopes of hx_paged_attention_biased */
+int hx_prefill_attention_biased(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                const int* request_start, const int* request_context,
+                                const int* request_table_row, const int* block_tables,
+                                int table_stride, void* out, int ldo, int requests,
+                                int tile_bound, int heads, int kv_heads, int head_dim,
+                                int page_size, int num_pages, float scale, int min_query_len,
+                                int window, int keep_first, int pack_heads, const float* sinks,
+                                const float* slopes, int* status, cudaStream_t stream);
 
 /* the same on tcgen05, scores and partial outputs in tensor memory (pages of 16, 32, 64) */
 int hx_prefill_attention_tc_supports(int head_dim, int page_size);
