@@ -436,6 +436,42 @@ def medolorn_config(shape: dict, options):
                           max_positions=shape["max_position_embeddings"])
 
 
+def rorovik_config(shape: dict, options):
+    """The Rorovik design with the layer sizes of a Llama shape: the same width, vocabulary and
+    active feed-forward size.  Layers in turn: attention (the shape's heads on a quarter as many
+    key/value heads, window ``--window`` or 1,024, query temperature, value mixing, sinks,
+    distance slopes, head gates), latent attention twice (the shape's heads, 64 rotated
+    coordinates behind the head size, a cached row of 192 + 64, queries through a latent of a
+    quarter of the width, stretched frequencies, causal), attention again.  The first layer's
+    feed-forward is dense with biases, the others are 16 routed experts of a quarter of the
+    shape's feed-forward of which a token uses 4 of 18 router outputs (two return their
+    input); a token input of 256 numbers in every layer."""
+    import math
+
+    from helix_runtime_b200.config.rorovik import (CausalLatentAttentionConfig, FeedForwardConfig,
+                                                   RorovikConfig, RorovikLayerConfig,
+                                                   RotaryScalingConfig, WindowedAttentionConfig)
+    heads, dim, width = shape["num_attention_heads"], shape["head_dim"], shape["hidden_size"]
+    ff = -(-shape["intermediate_size"] // 4 // 128) * 128
+    dense = FeedForwardConfig(kind="dense", ff=shape["intermediate_size"])
+    routed = FeedForwardConfig(kind="moe", ff=ff, experts=16, identity=2, top=4, limit=7.0)
+    attention = WindowedAttentionConfig(
+        heads=heads, kv_heads=options.kv_heads or max(1, heads // 4), dim=dim, vdim=dim,
+        scale=1.0 / math.sqrt(dim), window=options.window or 1024, temp_coef=0.1, temp_every=512,
+        v_mix=True)
+    latent = CausalLatentAttentionConfig(
+        heads=heads, dim=dim, rot_dim=64, vdim=dim, kv_rank=192, q_rank=width // 4,
+        scale=1.0 / math.sqrt(dim + 64), rot_base=500000.0, rot_dims=64,
+        scaling=RotaryScalingConfig(factor=8.0, original=1024, fast=32.0, slow=1.0))
+    kinds = (("attention", attention), ("latent_attention", latent), ("latent_attention", latent),
+             ("attention", attention))
+    layers = tuple(RorovikLayerConfig(*kinds[index % 4], dense if index == 0 else routed)
+                   for index in range(shape["num_hidden_layers"]))
+    return RorovikConfig(vocab=shape["vocab_size"], width=width, norm_eps=shape["rms_norm_eps"],
+                         residual_mult=0.5, side_dim=256, layers=layers,
+                         max_positions=shape["max_position_embeddings"])
+
+
 def compare_designs(options, peaks, device) -> int:
     """``--compare``: the Rekasun design beside the Llama design at equal layer sizes
     (``--compare zuzadra``: and the Zuzadra design beside both), a few
@@ -526,11 +562,15 @@ def compare_designs(options, peaks, device) -> int:
         shape = dict(SHAPES[name], num_hidden_layers=layers)
         row = {"hidden": shape["hidden_size"], "heads": shape["num_attention_heads"],
                "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"]}
-        designs = [("llama", LlamaConfig(**shape)), ("rekasun", rekasun_config(shape, options))]
+        designs = [("llama", LlamaConfig(**shape))]
+        if options.compare != "rorovik":
+            designs.append(("rekasun", rekasun_config(shape, options)))
         if options.compare in ("zuzadra", "medolorn"):
             designs.append(("zuzadra", zuzadra_config(shape, options)))
-        if options.compare == "medolorn":
+        if options.compare in ("medolorn", "rorovik"):
             designs.append(("medolorn", medolorn_config(shape, options)))
+        if options.compare == "rorovik":
+            designs.append(("rorovik", rorovik_config(shape, options)))
         for design, config in designs:
             model = random_model(config, seed=0, dtype="bfloat16", device=device)
             row[design] = measure(model)
@@ -538,10 +578,11 @@ def compare_designs(options, peaks, device) -> int:
             torch.cuda.empty_cache()
         shapes[name] = row
     print(json.dumps({
-        "metric": "prefill and decode throughput, " + {"zuzadra": "Zuzadra and ",
-                                                        "medolorn": "Medolorn, Zuzadra and "}
-                  .get(options.compare, "") +
-                  "Rekasun design beside Llama design (bf16)",
+        "metric": "prefill and decode throughput, " + {"zuzadra": "Zuzadra and Rekasun",
+                                                        "medolorn": "Medolorn, Zuzadra and Rekasun",
+                                                        "rorovik": "Rorovik and Medolorn"}
+                  .get(options.compare, "Rekasun") +
+                  " design beside Llama design (bf16)",
         "layers": layers, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
         "rekasun": {"window": options.window, "keep_first": options.keep_first,
                     "taps": options.taps, "kv_heads": options.kv_heads or "as query heads"},
@@ -574,16 +615,18 @@ def main() -> int:
     parser.add_argument("--shape", choices=tuple(SHAPES), default="llama-2-7b",
                         help="layer sizes for --serving, --profile and --timeline (the contract "
                              "line is always the Llama-2-7B shape)")
-    parser.add_argument("--design", choices=("llama", "rekasun", "zuzadra", "medolorn"), default="llama",
+    parser.add_argument("--design", choices=("llama", "rekasun", "zuzadra", "medolorn", "rorovik"),
+                        default="llama",
                         help="which decoder the layers of --shape are built as, for --profile "
                              "and --timeline (the contract line is always the Llama design)")
     parser.add_argument("--compare", nargs="?", const="rekasun", default=None,
-                        choices=("rekasun", "zuzadra", "medolorn"),
+                        choices=("rekasun", "zuzadra", "medolorn", "rorovik"),
                         help="prefill and decode throughput of the Rekasun design beside the "
                              "Llama design at equal layer sizes (a few layers of each --shape), "
                              "as one JSON line of its own; '--compare zuzadra' adds the Zuzadra "
                              "design as a third row, '--compare medolorn' the Medolorn design "
-                             "as a fourth")
+                             "as a fourth; '--compare rorovik' runs the Llama, Medolorn and "
+                             "Rorovik designs")
     parser.add_argument("--window", type=int, default=1024,
                         help="--design rekasun / --compare: keys a position sees behind itself")
     parser.add_argument("--keep-first", type=int, default=64,
@@ -642,6 +685,8 @@ def main() -> int:
         config = zuzadra_config(shape, options)
     elif options.design == "medolorn":
         config = medolorn_config(shape, options)
+    elif options.design == "rorovik":
+        config = rorovik_config(shape, options)
     model = random_model(config, seed=0, dtype="bfloat16", device=device)
     rng = np.random.default_rng(0)
     out_dir = options.log_dir or tempfile.mkdtemp(prefix="helix_bench_")

@@ -9,7 +9,7 @@
 //     factor on the query that grows with the logarithm of the position, values blended with
 //     the values an earlier layer computed for the same token, and the sigmoid of the head
 //     gates' sums; queries, keys and values leave in rows of row_dim per head (zeros behind
-//     the head's own coordinates);
+//     the head's own coordinates), keys and values straight into the cache pages;
 //   * hx_head_gate: every head of the attention's result times its token's gate;
 //   * hx_token_gate: g = gelu_tanh(s) * table[token][offset + c], the gate of a per-token
 //     input that is looked up in a table by the token's id.
@@ -58,6 +58,17 @@ struct NormedRowsArgs {
   int ld_rows;
   float* gates;                // [tokens, heads]: sigmoid of the gate sums; null: none
   int heads, kv_heads, head_dim, value_dim, row_dim;
+  // The cache append (k_cache null: keys and values go to `rows` instead): the token's keys
+  // and values are written to slot position % page_size of the page its request's block table
+  // names for position / page_size, in the cache's layout (hx_cache_offset).
+  const int* token_request;
+  const int* request_table_row;
+  const int* block_tables;
+  int table_stride;
+  T* k_cache;
+  T* v_cache;
+  int page_size, num_pages;
+  int* status;
 };
 
 template <typename T>
@@ -107,9 +118,22 @@ __global__ __launch_bounds__(256) void biased_normed_rows_kernel(const NormedRow
     }
     out[c] = hx_from_float<T>(v);
   }
-  // keys, then values
+  // keys, then values: into the pages, or behind the queries
   T* keys = out + a.heads * R;
   T* values = keys + a.kv_heads * R;
+  const bool append = a.k_cache != nullptr;
+  int page = -1, slot = 0;
+  if (append) {
+    const int position = a.positions[token];
+    const int table_row = a.request_table_row[a.token_request[token]];
+    page = a.block_tables[static_cast<size_t>(table_row) * a.table_stride + position / a.page_size];
+    slot = position % a.page_size;
+    if (page < 0 || page >= a.num_pages) {
+      if (threadIdx.x == 0 && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
+      page = -1;
+    }
+  }
+  const int chunk = hx_cache_chunk(sizeof(T), R);
   float* source = a.value_source == nullptr ? nullptr
                                             : a.value_source + static_cast<size_t>(token) * v_size;
   for (int c = threadIdx.x; c < a.kv_heads * R; c += blockDim.x) {
@@ -129,8 +153,14 @@ __global__ __launch_bounds__(256) void biased_normed_rows_kernel(const NormedRow
         v = (1.0f - a.lambda) * v + a.lambda * source[i];
       }
     }
-    keys[c] = hx_from_float<T>(k);
-    values[c] = hx_from_float<T>(v);
+    if (!append) {
+      keys[c] = hx_from_float<T>(k);
+      values[c] = hx_from_float<T>(v);
+    } else if (page >= 0) {
+      const size_t at = hx_cache_offset(page, head, slot, d, a.kv_heads, a.page_size, R, chunk);
+      a.k_cache[at] = hx_from_float<T>(k);
+      a.v_cache[at] = hx_from_float<T>(v);
+    }
   }
   if (a.gates != nullptr)
     for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
@@ -203,7 +233,9 @@ HX_API int hx_norm_residual_add(float* residual, const float* y, const float* we
 
 // projected float32 [tokens, ld_projected] = [heads * head_dim | kv_heads * head_dim | kv_heads *
 // value_dim | heads gate sums (when gates is not null)]; rows [tokens, ld_rows] in `dtype` =
-// [heads | kv_heads | kv_heads] rows of row_dim.  See NormedRowsArgs for the rest.
+// [heads | kv_heads | kv_heads] rows of row_dim; with k_cache the keys and values go to the
+// token's slot of its request's pages instead (the cache append of the other position
+// kernels) and only the queries to `rows`.  See NormedRowsArgs for the rest.
 HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                                  const float* q_bias, const float* k_bias, const float* v_bias,
                                  const float* q_weight, const float* k_weight, float eps,
@@ -211,14 +243,22 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                                  int value_mix, float lambda, float* value_source, void* rows,
                                  int ld_rows, float* gates, int dtype, int tokens, int heads,
                                  int kv_heads, int head_dim, int value_dim, int row_dim,
+                                 const int* token_request, const int* request_table_row,
+                                 const int* block_tables, int table_stride, void* k_cache,
+                                 void* v_cache, int page_size, int num_pages, int* status,
                                  cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && head_dim > 0 && value_dim > 0 &&
                  row_dim >= head_dim && row_dim >= value_dim,
              "hx_biased_normed_rows: bad sizes");
   HX_REQUIRE(ld_projected >= heads * head_dim + kv_heads * (head_dim + value_dim) +
                                  (gates != nullptr ? heads : 0) &&
-                 ld_rows >= (heads + 2 * kv_heads) * row_dim,
+                 ld_rows >= (heads + (k_cache == nullptr ? 2 * kv_heads : 0)) * row_dim,
              "hx_biased_normed_rows: bad strides");
+  HX_REQUIRE(k_cache == nullptr ||
+                 (v_cache != nullptr && token_request != nullptr && request_table_row != nullptr &&
+                  block_tables != nullptr && positions != nullptr && page_size > 0 &&
+                  num_pages > 0 && table_stride > 0),
+             "hx_biased_normed_rows: the cache append needs the step's description");
   HX_REQUIRE(value_mix >= 0 && value_mix <= 2 && (value_mix == 0 || value_source != nullptr),
              "hx_biased_normed_rows: value mixing needs its source buffer");
   HX_REQUIRE(temp_every >= 0 && (temp_every == 0 || positions != nullptr) &&
@@ -229,14 +269,21 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
     NormedRowsArgs<float> a{projected, ld_projected, clear, q_bias, k_bias, v_bias, q_weight,
                             k_weight, eps, positions, temp_coef, temp_every, value_mix, lambda,
                             value_source, static_cast<float*>(rows), ld_rows, gates, heads,
-                            kv_heads, head_dim, value_dim, row_dim};
+                            kv_heads, head_dim, value_dim, row_dim, token_request,
+                            request_table_row, block_tables, table_stride,
+                            static_cast<float*>(k_cache), static_cast<float*>(v_cache), page_size,
+                            num_pages, status};
     hx_launch(biased_normed_rows_kernel<float>, dim3(tokens), 256, 0, stream, a);
   } else if (dtype == HX_BF16) {
     NormedRowsArgs<__nv_bfloat16> a{projected, ld_projected, clear, q_bias, k_bias, v_bias,
                                     q_weight, k_weight, eps, positions, temp_coef, temp_every,
                                     value_mix, lambda, value_source,
                                     static_cast<__nv_bfloat16*>(rows), ld_rows, gates, heads,
-                                    kv_heads, head_dim, value_dim, row_dim};
+                                    kv_heads, head_dim, value_dim, row_dim, token_request,
+                                    request_table_row, block_tables, table_stride,
+                                    static_cast<__nv_bfloat16*>(k_cache),
+                                    static_cast<__nv_bfloat16*>(v_cache), page_size, num_pages,
+                                    status};
     hx_launch(biased_normed_rows_kernel<__nv_bfloat16>, dim3(tokens), 256, 0, stream, a);
   } else {
     HX_REQUIRE(false, "hx_biased_normed_rows: unknown dtype %d", dtype);

@@ -225,7 +225,8 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_biased_normed_rows.argtypes = [
         _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_float,
         _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
-        _c_int, _c_int, _c_int, _c_ptr]
+        _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
+        _c_ptr, _c_ptr]
     library.hx_head_gate.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr]
     library.hx_token_gate.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                       _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
@@ -1047,13 +1048,22 @@ def biased_normed_rows(projected: torch.Tensor, clear: bool, rows: torch.Tensor,
                        k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
                        temp_coef: float = 0.0, temp_every: int = 0, value_mix: int = 0,
                        mix: float = 0.0, value_source: Optional[torch.Tensor] = None,
-                       gates: Optional[torch.Tensor] = None) -> None:
+                       gates: Optional[torch.Tensor] = None,
+                       token_request: Optional[torch.Tensor] = None,
+                       request_table_row: Optional[torch.Tensor] = None,
+                       block_tables: Optional[torch.Tensor] = None,
+                       k_cache: Optional[torch.Tensor] = None,
+                       v_cache: Optional[torch.Tensor] = None, page_size: int = 0,
+                       num_pages: int = 0, status: Optional[torch.Tensor] = None) -> None:
     """From the float32 projection ``[q | k | v | head gate sums]`` of every token: biases, one RMS
     norm over all query coordinates and one over all key coordinates, the query times ``1 +
     temp_coef * ln(floor((p + 1) / temp_every) + 1)``, values kept in (``value_mix`` 1) or
     blended with (2: ``(1 - mix) v + mix * source``) ``value_source``; ``rows`` gets ``[heads |
     kv_heads | kv_heads]`` rows of ``row_dim`` and ``gates`` ``[tokens, heads]`` the sigmoid of
-    the gate sums.  ``clear``: the projection is an accumulator and is left zero."""
+    the gate sums.  ``clear``: the projection is an accumulator and is left zero.  With
+    ``k_cache`` and ``v_cache`` (and the step's ``token_request``, ``request_table_row``,
+    ``block_tables``) keys and values are appended to the token's pages instead of written to
+    ``rows``, which then holds the queries only."""
     _need(projected, torch.float32, "projected")
     for vector in (q_bias, k_bias, v_bias, q_weight, k_weight, value_source, gates):
         if vector is not None:
@@ -1065,7 +1075,9 @@ def biased_normed_rows(projected: torch.Tensor, clear: bool, rows: torch.Tensor,
         _ptr(v_bias), _ptr(q_weight), _ptr(k_weight), float(eps), positions.data_ptr(),
         float(temp_coef), int(temp_every), int(value_mix), float(mix), _ptr(value_source),
         rows.data_ptr(), rows.stride(0), _ptr(gates), dtype_code(rows.dtype), tokens, heads,
-        kv_heads, head_dim, value_dim, row_dim, _stream()))
+        kv_heads, head_dim, value_dim, row_dim, _ptr(token_request), _ptr(request_table_row),
+        _ptr(block_tables), block_tables.stride(0) if block_tables is not None else 0,
+        _ptr(k_cache), _ptr(v_cache), int(page_size), int(num_pages), _ptr(status), _stream()))
 
 
 def head_gate(context: torch.Tensor, gates: torch.Tensor, tokens: int, heads: int,

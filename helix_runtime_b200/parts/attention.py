@@ -444,9 +444,9 @@ class NormedProjectionAttention(PagedAttention):
       ``sigmoid(G x)_h``, ONE number per head (tensor ``g`` ``[heads, hidden]``).
 
     ``[q | k | v | g]`` is one product with float32 sums (a weight stream for few tokens); one
-    kernel then adds the biases, norms, scales, blends, takes the gates' sigmoid and writes
-    queries, keys and values in rows of ``row_dim``; the plain append, the paged attention with
-    its sinks and slopes, the gate and the output matrix follow.
+    kernel then adds the biases, norms, scales, blends, takes the gates' sigmoid, writes the
+    queries in rows of ``row_dim`` and appends keys and values to the token's pages; the paged
+    attention with its sinks and slopes, the gate and the output matrix follow.
     """
 
     def __init__(self, spec: PartSpec, hidden_size: int) -> None:
@@ -547,6 +547,7 @@ class NormedProjectionAttention(PagedAttention):
         # values of this step's tokens
         source = get(f"attention.value_source/{self.v_rows}", (ctx.capacity, self.v_rows),
                      torch.float32) if self.value_mix else None
+        write = cache.owns and cache.keys is not None
         if is_weight_stream(x, self.w_proj, n):
             projected = ctx.workspace.accumulator(f"attention.projected/{self.projected_size}",
                                                   (STREAMING_MAX_TOKENS, self.projected_size))
@@ -562,8 +563,15 @@ class NormedProjectionAttention(PagedAttention):
                                k_bias=self.k_bias, v_bias=self.v_bias, q_weight=self.q_norm,
                                k_weight=self.k_norm, eps=self.eps, temp_coef=self.temp_coef,
                                temp_every=self.temp_every, value_mix=self.value_mix, mix=self.mix,
-                               value_source=source, gates=gates)
-        self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)      # the plain append
+                               value_source=source, gates=gates,
+                               token_request=ctx.token_request, request_table_row=ctx.request_slot,
+                               block_tables=cache.block_tables,
+                               k_cache=cache.keys if write else None,
+                               v_cache=cache.values if write else None,
+                               page_size=cache.page_size, num_pages=cache.num_pages,
+                               status=ctx.status)
+        if not write:       # nothing of its own to append to: keys and values stay in the rows
+            self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
         self.attend(ctx, cache, qkv, context)
         if self.head_gated:
             ops.head_gate(context, gates, n, self.heads, self.row_dim)

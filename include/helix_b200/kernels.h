@@ -218,14 +218,17 @@ int hx_norm_residual_add(float* residual, const float* y, const float* weight, f
  * temp_every) + 1) (temp_every 0: none), value_mix 1: v is stored in value_source, 2: v <- (1 -
  * lambda) v + lambda value_source; rows = [heads | kv_heads | kv_heads] rows of row_dim in
  * `dtype`; gates (may be null) [tokens][heads] = sigmoid of the gate sums; clear: projected is
- * left zero */
+ * left zero; with k_cache the keys and values are appended to the token's pages (as
+ * hx_rope_append does) instead of written to `rows` */
 int hx_biased_normed_rows(float* projected, int ld_projected, int clear, const float* q_bias,
                           const float* k_bias, const float* v_bias, const float* q_weight,
                           const float* k_weight, float eps, const int* positions, float temp_coef,
                           int temp_every, int value_mix, float lambda, float* value_source,
                           void* rows, int ld_rows, float* gates, int dtype, int tokens, int heads,
                           int kv_heads, int head_dim, int value_dim, int row_dim,
-                          cudaStream_t stream);
+                          const int* token_request, const int* request_table_row,
+                          const int* block_tables, int table_stride, void* k_cache, void* v_cache,
+                          int page_size, int num_pages, int* status, cudaStream_t stream);
 /* context[t][h * row_dim + c] *= gates[t][h] */
 int hx_head_gate(void* context, int ld_context, const float* gates, int dtype, int tokens,
                  int heads, int row_dim, cudaStream_t stream);

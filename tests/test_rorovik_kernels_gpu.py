@@ -234,6 +234,55 @@ def test_biases_whole_norms_temperature_value_mix_and_gates(heads, kv_heads, dim
             assert (left[:, :width] == 0).all() and (left[:, width:] == sums[:, width:]).all()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_keys_and_values_go_straight_into_the_pages(dtype):
+    """With the cache given, two requests' tokens land in the slots their block tables name (a
+    page's last slot, the next page's first), in the cache's own layout, padded coordinates as
+    zeros; slots of other tokens keep what they held, and the rows get the queries only."""
+    from helix_runtime_b200.ops import library as ops
+    from test_kernels_gpu import from_cache_layout
+    rng = np.random.default_rng(11)
+    heads, kv_heads, dim, vdim, row, page, pages = 2, 2, 6, 10, 16, 4, 7
+    positions = np.array([2, 3, 4, 9, 0])                  # three requests: 2, 3, 4; 9; 0
+    token_request = np.array([0, 0, 0, 1, 2])
+    slots = np.array([3, 1, 2])                             # block table rows of the requests
+    tables = np.full((4, 4), -1, dtype=np.int32)
+    tables[3, :2] = [5, 0]
+    tables[1, :3] = [6, 2, 4]
+    tables[2, :1] = [1]
+    width = heads * dim + kv_heads * (dim + vdim)
+    sums = held(rng.normal(size=(5, width)), torch.float32)
+    k_cache = torch.full((pages, kv_heads, page, row), 3.0, dtype=dtype, device="cuda")
+    v_cache = torch.full((pages, kv_heads, page, row), 4.0, dtype=dtype, device="cuda")
+    rows = torch.full((5, heads * row + 2), 7.0, dtype=dtype, device="cuda")
+    status = status_word()
+    ops.biased_normed_rows(device_tensor(sums), False, rows, 5, heads, kv_heads, dim, vdim, row,
+                           dev(positions, torch.int32), token_request=dev(token_request, torch.int32),
+                           request_table_row=dev(slots, torch.int32),
+                           block_tables=dev(tables, torch.int32), k_cache=k_cache, v_cache=v_cache,
+                           page_size=page, num_pages=pages, status=status)
+    assert int(status.item()) == 0
+    got_k = from_cache_layout(host(k_cache), dtype)
+    got_v = from_cache_layout(host(v_cache), dtype)
+    want_k = np.full((pages, kv_heads, page, row), 3.0)
+    want_v = np.full((pages, kv_heads, page, row), 4.0)
+    k = sums[:, heads * dim:(heads + kv_heads) * dim].reshape(5, kv_heads, dim)
+    v = sums[:, (heads + kv_heads) * dim:].reshape(5, kv_heads, vdim)
+    for token in range(5):
+        table_page = tables[slots[token_request[token]], positions[token] // page]
+        slot = positions[token] % page
+        want_k[table_page, :, slot] = 0.0
+        want_v[table_page, :, slot] = 0.0
+        want_k[table_page, :, slot, :dim] = held(k[token], dtype)
+        want_v[table_page, :, slot, :vdim] = held(v[token], dtype)
+    close(got_k, want_k, 0.0, what="keys in the pages")
+    close(got_v, want_v, 0.0, what="values in the pages")
+    got = as_double(rows)
+    assert (got[:, heads * row:] == 7.0).all(), "nothing is written behind the queries"
+    close(got[:, :heads * row].reshape(5, heads, row)[:, :, :dim],
+          held(sums[:, :heads * dim], dtype).reshape(5, heads, dim), 0.0, what="queries")
+
+
 def test_parts_of_the_projection_rule_may_be_absent():
     """No biases, no norm, no temperature, no gates: the rows are the sums, cut into heads."""
     from helix_runtime_b200.ops import library as ops
