@@ -93,6 +93,11 @@ struct TcPrefillArgs {
   int* status;
   int window;       // 0: every earlier key; else the query at p sees key j <= p with p - j < window
   int keep_first;   // ... or j < keep_first (with a window only)
+  // Optional, per query head (null: absent).  sinks: the softmax's denominator also holds
+  // exp(sinks[h]), a term without key or value.  slopes: the score of key j for the query at
+  // position i is lowered by slopes[h] * (i - j).
+  const float* sinks = nullptr;
+  const float* slopes = nullptr;
 };
 
 template <int D>
@@ -483,6 +488,8 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
     float row_max = -INFINITY;      // the reference of this row's exponentials, in log2 units
     float row_sum = 0.0f;
     const float scale_log2 = a.scale * 1.4426950408889634f;
+    // a slope per position of distance, in the same log2 units (0: none)
+    const float slope_log2 = a.slopes != nullptr ? a.slopes[head] * 1.4426950408889634f : 0.0f;
     bool ok = true;
 
     // One lane waits and looks at the failure flag, all lanes get the same answer (what
@@ -517,6 +524,12 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
           for (int i = 0; i < 16; ++i) p[c * 16 + i] = __uint_as_float(r[c][i]) * scale_log2;
       }
       const int key0 = tile_at(tile) * BLOCK_N;
+      if (a.slopes != nullptr) {
+        const float distance0 = static_cast<float>(q_position - key0);
+#pragma unroll
+        for (int i = 0; i < BLOCK_N; ++i)
+          p[i] = fmaf(-slope_log2, distance0 - static_cast<float>(i), p[i]);
+      }
       if (key0 + BLOCK_N - 1 > q_position) {
 #pragma unroll
         for (int i = 0; i < BLOCK_N; ++i)
@@ -636,7 +649,15 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
                     static_cast<uint32_t>((my_tiles - 1) / S_BUFFERS) & 1u);
       if (ok) {
         tc_fence_after();
-        const float inverse = 1.0f / row_sum;
+        float inverse = 1.0f / row_sum;
+        if (a.sinks != nullptr) {
+          // the sink joins the finished row: with M = max(m, s) the result is
+          // o 2^(m - M) / (l 2^(m - M) + 2^(s - M)), everything in log2 units
+          const float sink_log2 = a.sinks[head] * 1.4426950408889634f;
+          const float top = fmaxf(row_max, sink_log2);
+          const float keep = row_max == -INFINITY ? 0.0f : fast_exp2(row_max - top);
+          inverse = keep / (row_sum * keep + fast_exp2(sink_log2 - top));
+        }
         __nv_bfloat16* out = a.out +
                              static_cast<size_t>(q_begin + row0 + l * BLOCK_M + row) * a.ldo +
                              static_cast<size_t>(head) * D;
@@ -705,15 +726,17 @@ HX_API int hx_prefill_attention_tc_supports(int head_dim, int page_size) {
 
 // The arguments of hx_prefill_attention; tile_bound bounds the number of 256-token query tiles
 // (a larger bound only launches CTAs that leave at once).
-HX_API int hx_prefill_attention_tc_windowed(const void* q, int ldq, const void* k_cache,
-                                            const void* v_cache, const int* request_start,
-                                            const int* request_context,
-                                            const int* request_table_row, const int* block_tables,
-                                            int table_stride, void* out, int ldo, int requests,
-                                            int tile_bound, int heads, int kv_heads, int head_dim,
-                                            int page_size, int num_pages, float scale,
-                                            int min_query_len, int window, int keep_first,
-                                            int* status, cudaStream_t stream) {
+// ... and with the optional per-head sinks and distance slopes (see TcPrefillArgs; null: none).
+HX_API int hx_prefill_attention_tc_biased(const void* q, int ldq, const void* k_cache,
+                                          const void* v_cache, const int* request_start,
+                                          const int* request_context,
+                                          const int* request_table_row, const int* block_tables,
+                                          int table_stride, void* out, int ldo, int requests,
+                                          int tile_bound, int heads, int kv_heads, int head_dim,
+                                          int page_size, int num_pages, float scale,
+                                          int min_query_len, int window, int keep_first,
+                                          const float* sinks, const float* slopes, int* status,
+                                          cudaStream_t stream) {
   HX_REQUIRE(window >= 0 && keep_first >= 0, "hx_prefill_attention_tc: bad window");
   if (window == 0) keep_first = 0;
   HX_REQUIRE(hx_prefill_attention_tc_supports(head_dim, page_size),
@@ -735,7 +758,7 @@ HX_API int hx_prefill_attention_tc_windowed(const void* q, int ldq, const void* 
                   static_cast<const __nv_bfloat16*>(v_cache), request_start, request_context,
                   request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(out),
                   ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status,
-                  window, keep_first};
+                  window, keep_first, sinks, slopes};
   int rc;
   switch (head_dim) {
     case 64: rc = launch<64>(a, tile_bound, stream); break;
@@ -747,6 +770,22 @@ HX_API int hx_prefill_attention_tc_windowed(const void* q, int ldq, const void* 
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_prefill_attention_tc");
   return HX_OK;
+}
+
+HX_API int hx_prefill_attention_tc_windowed(const void* q, int ldq, const void* k_cache,
+                                            const void* v_cache, const int* request_start,
+                                            const int* request_context,
+                                            const int* request_table_row, const int* block_tables,
+                                            int table_stride, void* out, int ldo, int requests,
+                                            int tile_bound, int heads, int kv_heads, int head_dim,
+                                            int page_size, int num_pages, float scale,
+                                            int min_query_len, int window, int keep_first,
+                                            int* status, cudaStream_t stream) {
+  return hx_prefill_attention_tc_biased(q, ldq, k_cache, v_cache, request_start, request_context,
+                                        request_table_row, block_tables, table_stride, out, ldo,
+                                        requests, tile_bound, heads, kv_heads, head_dim, page_size,
+                                        num_pages, scale, min_query_len, window, keep_first,
+                                        nullptr, nullptr, status, stream);
 }
 
 // Every earlier key (no window).

@@ -17,22 +17,77 @@
 
 namespace {
 
+// A thread holds its share of the row in registers between the two passes (up to
+// NORM_ADD_QUADS float4 pieces; wider rows read the rest again), and all of its loads are in
+// flight together: with a few dozen tokens the kernel is a handful of round trips to memory.
+constexpr int NORM_ADD_THREADS = 256;
+constexpr int NORM_ADD_QUADS = 8;       // 256 threads x 8 x 4 floats: rows up to 8,192 wide
+
 template <typename T>
-__global__ __launch_bounds__(256) void norm_residual_add_kernel(
+__global__ __launch_bounds__(NORM_ADD_THREADS) void norm_residual_add_kernel(
     float* __restrict__ residual, const float* __restrict__ y, const float* __restrict__ weight,
     float eps, float mult, T* __restrict__ cast_out, int ld_cast, int width) {
   __shared__ float scratch[32];
   hx_pdl_prologue();
   const size_t row = static_cast<size_t>(blockIdx.x) * width;
+  T* cast = cast_out == nullptr ? nullptr : cast_out + static_cast<size_t>(blockIdx.x) * ld_cast;
+  const bool wide = (width & 3) == 0 &&
+                    ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(y) |
+                      reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+  if (wide && width <= NORM_ADD_THREADS * NORM_ADD_QUADS * 4) {
+    const int quads = width >> 2;
+    float4 held[NORM_ADD_QUADS];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NORM_ADD_QUADS; ++i) {
+      const int q = threadIdx.x + i * NORM_ADD_THREADS;
+      held[i] = q < quads ? *reinterpret_cast<const float4*>(y + row + 4 * q)
+                          : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+#pragma unroll
+    for (int i = 0; i < NORM_ADD_QUADS; ++i) {
+      sum = fmaf(held[i].x, held[i].x, sum); sum = fmaf(held[i].y, held[i].y, sum);
+      sum = fmaf(held[i].z, held[i].z, sum); sum = fmaf(held[i].w, held[i].w, sum);
+    }
+    const float inverse =
+        mult / sqrtf(hx_block_sum(sum, scratch) / static_cast<float>(width) + eps);
+    float4 w[NORM_ADD_QUADS], x[NORM_ADD_QUADS];
+#pragma unroll
+    for (int i = 0; i < NORM_ADD_QUADS; ++i) {
+      const int q = threadIdx.x + i * NORM_ADD_THREADS;
+      if (q < quads) {
+        w[i] = *reinterpret_cast<const float4*>(weight + 4 * q);
+        x[i] = *reinterpret_cast<const float4*>(residual + row + 4 * q);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NORM_ADD_QUADS; ++i) {
+      const int q = threadIdx.x + i * NORM_ADD_THREADS;
+      if (q >= quads) continue;
+      x[i].x = fmaf(held[i].x * inverse, w[i].x, x[i].x);
+      x[i].y = fmaf(held[i].y * inverse, w[i].y, x[i].y);
+      x[i].z = fmaf(held[i].z * inverse, w[i].z, x[i].z);
+      x[i].w = fmaf(held[i].w * inverse, w[i].w, x[i].w);
+      *reinterpret_cast<float4*>(residual + row + 4 * q) = x[i];
+      if (cast != nullptr) {
+        cast[4 * q] = hx_from_float<T>(x[i].x);
+        cast[4 * q + 1] = hx_from_float<T>(x[i].y);
+        cast[4 * q + 2] = hx_from_float<T>(x[i].z);
+        cast[4 * q + 3] = hx_from_float<T>(x[i].w);
+      }
+    }
+    return;
+  }
   float sum = 0.0f;
+#pragma unroll 4
   for (int c = threadIdx.x; c < width; c += blockDim.x) sum = fmaf(y[row + c], y[row + c], sum);
   const float inverse =
       mult / sqrtf(hx_block_sum(sum, scratch) / static_cast<float>(width) + eps);
+#pragma unroll 4
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float x = fmaf(y[row + c] * inverse, weight[c], residual[row + c]);
     residual[row + c] = x;
-    if (cast_out != nullptr)
-      cast_out[static_cast<size_t>(blockIdx.x) * ld_cast + c] = hx_from_float<T>(x);
+    if (cast != nullptr) cast[c] = hx_from_float<T>(x);
   }
 }
 
@@ -71,8 +126,12 @@ struct NormedRowsArgs {
   int* status;
 };
 
+// Few tokens (decoding) are few CTAs: a CTA of 1,024 threads then walks a token's row in a
+// quarter of the round trips; with many tokens 256 threads leave room for several CTAs an SM.
+constexpr int NORMED_ROWS_FEW_TOKENS = 512;
+
 template <typename T>
-__global__ __launch_bounds__(256) void biased_normed_rows_kernel(const NormedRowsArgs<T> a) {
+__global__ __launch_bounds__(1024) void biased_normed_rows_kernel(const NormedRowsArgs<T> a) {
   __shared__ float scratch[32];
   hx_pdl_prologue();
   const int token = blockIdx.x;
@@ -87,6 +146,7 @@ __global__ __launch_bounds__(256) void biased_normed_rows_kernel(const NormedRow
   float q_inverse = 1.0f, k_inverse = 1.0f;
   if (a.q_weight != nullptr) {
     float sum = 0.0f;
+#pragma unroll 4
     for (int c = threadIdx.x; c < q_size; c += blockDim.x) {
       const float v = biased(c, a.q_bias, 0);
       sum = fmaf(v, v, sum);
@@ -95,6 +155,7 @@ __global__ __launch_bounds__(256) void biased_normed_rows_kernel(const NormedRow
   }
   if (a.k_weight != nullptr) {
     float sum = 0.0f;
+#pragma unroll 4
     for (int c = threadIdx.x; c < k_size; c += blockDim.x) {
       const float v = biased(c, a.k_bias, q_size);
       sum = fmaf(v, v, sum);
@@ -107,6 +168,7 @@ __global__ __launch_bounds__(256) void biased_normed_rows_kernel(const NormedRow
         logf(static_cast<float>((a.positions[token] + 1) / a.temp_every) + 1.0f);
   const int D = a.head_dim, R = a.row_dim, E = a.value_dim;
   // queries
+#pragma unroll 4
   for (int c = threadIdx.x; c < a.heads * R; c += blockDim.x) {
     const int head = c / R, d = c - head * R;
     float v = 0.0f;
@@ -136,6 +198,7 @@ __global__ __launch_bounds__(256) void biased_normed_rows_kernel(const NormedRow
   const int chunk = hx_cache_chunk(sizeof(T), R);
   float* source = a.value_source == nullptr ? nullptr
                                             : a.value_source + static_cast<size_t>(token) * v_size;
+#pragma unroll 4
   for (int c = threadIdx.x; c < a.kv_heads * R; c += blockDim.x) {
     const int head = c / R, d = c - head * R;
     float k = 0.0f, v = 0.0f;
@@ -219,10 +282,10 @@ HX_API int hx_norm_residual_add(float* residual, const float* y, const float* we
   HX_REQUIRE(cast_out == nullptr || ld_cast >= width, "hx_norm_residual_add: bad stride");
   if (tokens == 0) return HX_OK;
   if (dtype == HX_F32) {
-    hx_launch(norm_residual_add_kernel<float>, dim3(tokens), 256, 0, stream, residual, y, weight,
+    hx_launch(norm_residual_add_kernel<float>, dim3(tokens), NORM_ADD_THREADS, 0, stream, residual, y, weight,
               eps, mult, static_cast<float*>(cast_out), ld_cast, width);
   } else if (dtype == HX_BF16) {
-    hx_launch(norm_residual_add_kernel<__nv_bfloat16>, dim3(tokens), 256, 0, stream, residual, y,
+    hx_launch(norm_residual_add_kernel<__nv_bfloat16>, dim3(tokens), NORM_ADD_THREADS, 0, stream, residual, y,
               weight, eps, mult, static_cast<__nv_bfloat16*>(cast_out), ld_cast, width);
   } else {
     HX_REQUIRE(false, "hx_norm_residual_add: unknown dtype %d", dtype);
@@ -265,6 +328,7 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                  ((q_weight == nullptr && k_weight == nullptr) || eps > 0.0f),
              "hx_biased_normed_rows: bad constants");
   if (tokens == 0) return HX_OK;
+  const int threads = tokens <= NORMED_ROWS_FEW_TOKENS ? 1024 : 256;
   if (dtype == HX_F32) {
     NormedRowsArgs<float> a{projected, ld_projected, clear, q_bias, k_bias, v_bias, q_weight,
                             k_weight, eps, positions, temp_coef, temp_every, value_mix, lambda,
@@ -273,7 +337,7 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                             request_table_row, block_tables, table_stride,
                             static_cast<float*>(k_cache), static_cast<float*>(v_cache), page_size,
                             num_pages, status};
-    hx_launch(biased_normed_rows_kernel<float>, dim3(tokens), 256, 0, stream, a);
+    hx_launch(biased_normed_rows_kernel<float>, dim3(tokens), threads, 0, stream, a);
   } else if (dtype == HX_BF16) {
     NormedRowsArgs<__nv_bfloat16> a{projected, ld_projected, clear, q_bias, k_bias, v_bias,
                                     q_weight, k_weight, eps, positions, temp_coef, temp_every,
@@ -284,7 +348,7 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                                     static_cast<__nv_bfloat16*>(k_cache),
                                     static_cast<__nv_bfloat16*>(v_cache), page_size, num_pages,
                                     status};
-    hx_launch(biased_normed_rows_kernel<__nv_bfloat16>, dim3(tokens), 256, 0, stream, a);
+    hx_launch(biased_normed_rows_kernel<__nv_bfloat16>, dim3(tokens), threads, 0, stream, a);
   } else {
     HX_REQUIRE(false, "hx_biased_normed_rows: unknown dtype %d", dtype);
   }

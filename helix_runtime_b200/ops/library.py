@@ -220,6 +220,9 @@ def _declare(library: ctypes.CDLL) -> None:
         _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]
     library.hx_prefill_attention_biased.argtypes = [
         *library.hx_prefill_attention_windowed.argtypes[:-2], _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_prefill_attention_tc_biased.argtypes = [
+        *library.hx_prefill_attention_windowed.argtypes[:-2], _c_ptr, _c_ptr, _c_ptr, _c_ptr]
+    library.hx_prefill_attention_tc_biased.restype = _c_int
     library.hx_norm_residual_add.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_float, _c_float, _c_ptr,
                                              _c_int, _c_int, _c_int, _c_int, _c_ptr]
     library.hx_biased_normed_rows.argtypes = [
@@ -662,14 +665,12 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     ``packed``: the ``mma.sync`` kernel with the heads of a key/value head side by side in a
     tile's rows (``prefill_attention_packed_tokens`` tokens a tile), which reads keys and
     values once for all of them; it takes single decoded tokens as well.  ``sinks`` and
-    ``slopes`` as in :func:`paged_attention`; with either the ``mma.sync`` kernel runs."""
+    ``slopes`` as in :func:`paged_attention`; all three kernels take them."""
     biased = sinks is not None or slopes is not None
     for per_head in (sinks, slopes):
         if per_head is not None:
             _need(per_head, torch.float32, "sinks and slopes")
             assert per_head.numel() == heads
-    if biased:
-        tensor_memory = False
     _need(q, torch.bfloat16, "q")
     _need(k_cache, torch.bfloat16, "k_cache")
     _need(out, torch.bfloat16, "out")
@@ -690,7 +691,11 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         request_context.data_ptr(), request_table_row.data_ptr(), block_tables.data_ptr(),
         block_tables.stride(0), out.data_ptr(), out.stride(0), requests, tile_bound, heads,
         kv_heads, head_dim, page_size, num_pages, float(scale), min_query_len)
-    if biased:
+    if biased and tensor_memory:
+        _check(lib().hx_prefill_attention_tc_biased(*arguments, int(window), int(keep_first),
+                                                    _ptr(sinks), _ptr(slopes), _ptr(status),
+                                                    _stream()))
+    elif biased:
         _check(lib().hx_prefill_attention_biased(*arguments, int(window), int(keep_first),
                                                  1 if packed else 0, _ptr(sinks), _ptr(slopes),
                                                  _ptr(status), _stream()))

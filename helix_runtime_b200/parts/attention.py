@@ -116,6 +116,7 @@ def stretched_frequencies(dims: int, theta: float, scaling: Optional[Mapping[str
 
 class PagedAttention(Mixer):
     pack_heads = False      # subclasses whose heads share few cached rows set this
+    pack_always = True      # ... for every step; False: only for steps of single tokens
 
     def __init__(self, spec: PartSpec, hidden_size: int) -> None:
         super().__init__(spec, hidden_size)
@@ -343,6 +344,7 @@ class PagedAttention(Mixer):
         # many heads on one cached row: the kernel whose rows are a token's heads reads the
         # row once for all of them, decoded tokens included
         if (self.pack_heads and ctx.dtype == torch.bfloat16
+                and (self.pack_always or ctx.max_query_len < TENSOR_CORE_MIN_QUERY)
                 and ops.prefill_attention_supports(self.row_dim, cache.page_size)
                 and ops.prefill_attention_packed_tokens(self.heads, self.kv_heads) > 0):
             ops.prefill_attention(qkv, cache.keys, cache.values, ctx.request_start,
@@ -459,6 +461,11 @@ class NormedProjectionAttention(PagedAttention):
         if self.conv_taps > 1:
             raise ValueError("this part has no filter over time")
         self.spec = spec
+        # decoding: query heads that share a key/value head attend side by side in a tile's
+        # rows (the streaming kernel would read the shared keys once per query head); steps
+        # with prompt portions keep the kernels every attention part uses
+        self.pack_heads = self.heads // self.kv_heads >= 2
+        self.pack_always = False
         self.head_gated = gate is not None
         self.bias = bool(spec.get("bias", False))
         norm = spec.get("whole_norm")

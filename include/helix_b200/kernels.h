@@ -466,6 +466,16 @@ int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache, const v
                             int table_stride, void* out, int ldo, int requests, int tile_bound,
                             int heads, int kv_heads, int head_dim, int page_size, int num_pages,
                             float scale, int min_query_len, int* status, cudaStream_t stream);
+/* hx_prefill_attention_tc_windowed with the optional sinks and slopes of
+ * hx_paged_attention_biased */
+int hx_prefill_attention_tc_biased(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                   const int* request_start, const int* request_context,
+                                   const int* request_table_row, const int* block_tables,
+                                   int table_stride, void* out, int ldo, int requests,
+                                   int tile_bound, int heads, int kv_heads, int head_dim,
+                                   int page_size, int num_pages, float scale, int min_query_len,
+                                   int window, int keep_first, const float* sinks,
+                                   const float* slopes, int* status, cudaStream_t stream);
 /* the tcgen05 kernel with a window and kept first keys (see hx_prefill_attention_windowed) */
 int hx_prefill_attention_tc_windowed(const void* q, int ldq, const void* k_cache,
                                      const void* v_cache, const int* request_start,
