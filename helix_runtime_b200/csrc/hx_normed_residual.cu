@@ -167,18 +167,20 @@ __global__ __launch_bounds__(1024) void biased_normed_rows_kernel(const NormedRo
     temperature = 1.0f + a.temp_coef *
         logf(static_cast<float>((a.positions[token] + 1) / a.temp_every) + 1.0f);
   const int D = a.head_dim, R = a.row_dim, E = a.value_dim;
-  // queries
+  // queries: a warp takes a head at a time, its lanes the head's coordinates
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int head = warp; head < a.heads; head += warps) {
 #pragma unroll 4
-  for (int c = threadIdx.x; c < a.heads * R; c += blockDim.x) {
-    const int head = c / R, d = c - head * R;
-    float v = 0.0f;
-    if (d < D) {
-      const int i = head * D + d;
-      v = biased(i, a.q_bias, 0) * q_inverse;
-      if (a.q_weight != nullptr) v *= a.q_weight[i];
-      v *= temperature;
+    for (int d = lane; d < R; d += 32) {
+      float v = 0.0f;
+      if (d < D) {
+        const int i = head * D + d;
+        v = biased(i, a.q_bias, 0) * q_inverse;
+        if (a.q_weight != nullptr) v *= a.q_weight[i];
+        v *= temperature;
+      }
+      out[head * R + d] = hx_from_float<T>(v);
     }
-    out[c] = hx_from_float<T>(v);
   }
   // keys, then values: into the pages, or behind the queries
   T* keys = out + a.heads * R;
@@ -198,9 +200,10 @@ __global__ __launch_bounds__(1024) void biased_normed_rows_kernel(const NormedRo
   const int chunk = hx_cache_chunk(sizeof(T), R);
   float* source = a.value_source == nullptr ? nullptr
                                             : a.value_source + static_cast<size_t>(token) * v_size;
+  for (int head = warp; head < a.kv_heads; head += warps)
 #pragma unroll 4
-  for (int c = threadIdx.x; c < a.kv_heads * R; c += blockDim.x) {
-    const int head = c / R, d = c - head * R;
+  for (int d = lane; d < R; d += 32) {
+    const int c = head * R + d;
     float k = 0.0f, v = 0.0f;
     if (d < D) {
       const int i = head * D + d;
@@ -236,17 +239,21 @@ __global__ __launch_bounds__(1024) void biased_normed_rows_kernel(const NormedRo
   }
 }
 
-// grid (tokens, heads)
+// grid (tokens): a warp takes a head at a time
 template <typename T>
-__global__ __launch_bounds__(64) void head_gate_kernel(T* __restrict__ context, int ld_context,
-                                                       const float* __restrict__ gates,
-                                                       int heads, int row_dim) {
+__global__ __launch_bounds__(256) void head_gate_kernel(T* __restrict__ context, int ld_context,
+                                                        const float* __restrict__ gates,
+                                                        int heads, int row_dim) {
   hx_pdl_prologue();
-  const int token = blockIdx.x, head = blockIdx.y;
-  const float gate = gates[static_cast<size_t>(token) * heads + head];
-  T* row = context + static_cast<size_t>(token) * ld_context + head * row_dim;
-  for (int c = threadIdx.x; c < row_dim; c += blockDim.x)
-    row[c] = hx_from_float<T>(hx_to_float<T>(row[c]) * gate);
+  const int token = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  T* row = context + static_cast<size_t>(token) * ld_context;
+  for (int head = warp; head < heads; head += warps) {
+    const float gate = gates[static_cast<size_t>(token) * heads + head];
+#pragma unroll 4
+    for (int c = lane; c < row_dim; c += 32)
+      row[head * row_dim + c] = hx_from_float<T>(hx_to_float<T>(row[head * row_dim + c]) * gate);
+  }
 }
 
 // grid (tokens)
@@ -359,14 +366,14 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
 // context[t][h * row_dim + c] *= gates[t][h]; context in `dtype`, gates float32 [tokens, heads].
 HX_API int hx_head_gate(void* context, int ld_context, const float* gates, int dtype, int tokens,
                         int heads, int row_dim, cudaStream_t stream) {
-  HX_REQUIRE(tokens >= 0 && heads > 0 && heads <= 65535 && row_dim > 0 &&
+  HX_REQUIRE(tokens >= 0 && heads > 0 && row_dim > 0 &&
                  ld_context >= heads * row_dim, "hx_head_gate: bad sizes");
   if (tokens == 0) return HX_OK;
   if (dtype == HX_F32) {
-    hx_launch(head_gate_kernel<float>, dim3(tokens, heads), 64, 0, stream,
+    hx_launch(head_gate_kernel<float>, dim3(tokens), 256, 0, stream,
               static_cast<float*>(context), ld_context, gates, heads, row_dim);
   } else if (dtype == HX_BF16) {
-    hx_launch(head_gate_kernel<__nv_bfloat16>, dim3(tokens, heads), 64, 0, stream,
+    hx_launch(head_gate_kernel<__nv_bfloat16>, dim3(tokens), 256, 0, stream,
               static_cast<__nv_bfloat16*>(context), ld_context, gates, heads, row_dim);
   } else {
     HX_REQUIRE(false, "hx_head_gate: unknown dtype %d", dtype);
