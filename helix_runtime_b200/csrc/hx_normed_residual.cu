@@ -126,65 +126,47 @@ struct NormedRowsArgs {
   int* status;
 };
 
-// Few tokens (decoding) are few CTAs: a CTA of 1,024 threads then walks a token's row in a
-// quarter of the round trips; with many tokens 256 threads leave room for several CTAs an SM.
-constexpr int NORMED_ROWS_FEW_TOKENS = 512;
+// floor(n / d) for n * d < 2^32 as one multiplication: m = ceil(2^32 / d) (d > 1).
+struct FastDivisor {
+  unsigned d, m;
+  __device__ __forceinline__ int quotient(int n) const {
+    return d == 1u ? n : static_cast<int>(__umulhi(static_cast<unsigned>(n), m));
+  }
+};
+inline FastDivisor fast_divisor(int d) {
+  FastDivisor f;
+  f.d = static_cast<unsigned>(d);
+  f.m = d > 1 ? static_cast<unsigned>(((1ull << 32) + d - 1) / d) : 0u;
+  return f;
+}
+
+// A thread keeps its share of the token's queries and keys in registers between the pass that
+// sums their squares and the pass that writes them (NORMED_Q_HELD and NORMED_K_HELD numbers a
+// thread; wider projections read the sums again), so all of its loads of a pass are in flight
+// together and a token costs a handful of round trips.
+constexpr int NORMED_ROWS_THREADS = 512;
+constexpr int NORMED_Q_HELD = 16;       // 512 threads: queries up to 8,192 numbers a token
+constexpr int NORMED_K_HELD = 8;        // keys up to 4,096
 
 template <typename T>
-__global__ __launch_bounds__(1024) void biased_normed_rows_kernel(const NormedRowsArgs<T> a) {
+__global__ __launch_bounds__(NORMED_ROWS_THREADS) void biased_normed_rows_kernel(
+    const NormedRowsArgs<T> a, const FastDivisor by_dim, const FastDivisor by_value_dim) {
   __shared__ float scratch[32];
   hx_pdl_prologue();
   const int token = blockIdx.x;
+  const int tid = threadIdx.x, threads = blockDim.x;
   float* in = a.projected + static_cast<size_t>(token) * a.ld_projected;
   T* out = a.rows + static_cast<size_t>(token) * a.ld_rows;
-  const int q_size = a.heads * a.head_dim;
-  const int k_size = a.kv_heads * a.head_dim;
-  const int v_size = a.kv_heads * a.value_dim;
-  auto biased = [&](int c, const float* bias, int base) {
-    return in[base + c] + (bias != nullptr ? bias[c] : 0.0f);
-  };
-  float q_inverse = 1.0f, k_inverse = 1.0f;
-  if (a.q_weight != nullptr) {
-    float sum = 0.0f;
-#pragma unroll 4
-    for (int c = threadIdx.x; c < q_size; c += blockDim.x) {
-      const float v = biased(c, a.q_bias, 0);
-      sum = fmaf(v, v, sum);
-    }
-    q_inverse = 1.0f / sqrtf(hx_block_sum(sum, scratch) / static_cast<float>(q_size) + a.eps);
-  }
-  if (a.k_weight != nullptr) {
-    float sum = 0.0f;
-#pragma unroll 4
-    for (int c = threadIdx.x; c < k_size; c += blockDim.x) {
-      const float v = biased(c, a.k_bias, q_size);
-      sum = fmaf(v, v, sum);
-    }
-    k_inverse = 1.0f / sqrtf(hx_block_sum(sum, scratch) / static_cast<float>(k_size) + a.eps);
-  }
-  float temperature = 1.0f;
-  if (a.temp_every > 0)
-    temperature = 1.0f + a.temp_coef *
-        logf(static_cast<float>((a.positions[token] + 1) / a.temp_every) + 1.0f);
   const int D = a.head_dim, R = a.row_dim, E = a.value_dim;
-  // queries: a warp takes a head at a time, its lanes the head's coordinates
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int head = warp; head < a.heads; head += warps) {
-#pragma unroll 4
-    for (int d = lane; d < R; d += 32) {
-      float v = 0.0f;
-      if (d < D) {
-        const int i = head * D + d;
-        v = biased(i, a.q_bias, 0) * q_inverse;
-        if (a.q_weight != nullptr) v *= a.q_weight[i];
-        v *= temperature;
-      }
-      out[head * R + d] = hx_from_float<T>(v);
-    }
-  }
-  // keys, then values: into the pages, or behind the queries
-  T* keys = out + a.heads * R;
-  T* values = keys + a.kv_heads * R;
+  const int q_size = a.heads * D;
+  const int k_size = a.kv_heads * D;
+  const int v_size = a.kv_heads * E;
+  const float* k_in = in + q_size;
+  const float* v_in = k_in + k_size;
+  const bool held = q_size <= NORMED_Q_HELD * threads && k_size <= NORMED_K_HELD * threads;
+
+  // ---- where keys and values go: the token's slot of its page, or behind the queries (a
+  // chain of four dependent loads, started first so that it runs beside the row's own loads)
   const bool append = a.k_cache != nullptr;
   int page = -1, slot = 0;
   if (append) {
@@ -193,67 +175,150 @@ __global__ __launch_bounds__(1024) void biased_normed_rows_kernel(const NormedRo
     page = a.block_tables[static_cast<size_t>(table_row) * a.table_stride + position / a.page_size];
     slot = position % a.page_size;
     if (page < 0 || page >= a.num_pages) {
-      if (threadIdx.x == 0 && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
+      if (tid == 0 && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
       page = -1;
     }
   }
+  // ---- biased sums, and the sums of their squares
+  float q[NORMED_Q_HELD], k[NORMED_K_HELD];
+  float q_sum = 0.0f, k_sum = 0.0f;
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < NORMED_Q_HELD; ++i) {
+      const int c = tid + i * threads;
+      q[i] = c < q_size ? in[c] + (a.q_bias != nullptr ? a.q_bias[c] : 0.0f) : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < NORMED_K_HELD; ++i) {
+      const int c = tid + i * threads;
+      k[i] = c < k_size ? k_in[c] + (a.k_bias != nullptr ? a.k_bias[c] : 0.0f) : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < NORMED_Q_HELD; ++i) q_sum = fmaf(q[i], q[i], q_sum);
+#pragma unroll
+    for (int i = 0; i < NORMED_K_HELD; ++i) k_sum = fmaf(k[i], k[i], k_sum);
+  } else {
+#pragma unroll 4
+    for (int c = tid; c < q_size; c += threads) {
+      const float v = in[c] + (a.q_bias != nullptr ? a.q_bias[c] : 0.0f);
+      q_sum = fmaf(v, v, q_sum);
+    }
+#pragma unroll 4
+    for (int c = tid; c < k_size; c += threads) {
+      const float v = k_in[c] + (a.k_bias != nullptr ? a.k_bias[c] : 0.0f);
+      k_sum = fmaf(v, v, k_sum);
+    }
+  }
+  float q_factor = 1.0f, k_factor = 1.0f;
+  if (a.q_weight != nullptr)
+    q_factor = 1.0f / sqrtf(hx_block_sum(q_sum, scratch) / static_cast<float>(q_size) + a.eps);
+  if (a.k_weight != nullptr)
+    k_factor = 1.0f / sqrtf(hx_block_sum(k_sum, scratch) / static_cast<float>(k_size) + a.eps);
+  if (a.temp_every > 0)
+    q_factor *= 1.0f + a.temp_coef *
+        logf(static_cast<float>((a.positions[token] + 1) / a.temp_every) + 1.0f);
+
   const int chunk = hx_cache_chunk(sizeof(T), R);
+  T* key_rows = out + a.heads * R;
+  T* value_rows = key_rows + a.kv_heads * R;
+  auto put = [&](T* cache, T* rows, int head, int d, float value) {
+    if (!append) {
+      rows[head * R + d] = hx_from_float<T>(value);
+    } else if (page >= 0) {
+      cache[hx_cache_offset(page, head, slot, d, a.kv_heads, a.page_size, R, chunk)] =
+          hx_from_float<T>(value);
+    }
+  };
+
+  // ---- queries and keys: element c of the projection is coordinate c % D of head c / D
+  auto write_q = [&](int c, float value) {
+    const int head = by_dim.quotient(c);
+    if (a.q_weight != nullptr) value *= a.q_weight[c];
+    out[head * R + (c - head * D)] = hx_from_float<T>(value * q_factor);
+  };
+  auto write_k = [&](int c, float value) {
+    const int head = by_dim.quotient(c);
+    if (a.k_weight != nullptr) value *= a.k_weight[c];
+    put(a.k_cache, key_rows, head, c - head * D, value * k_factor);
+  };
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < NORMED_Q_HELD; ++i) {
+      const int c = tid + i * threads;
+      if (c < q_size) write_q(c, q[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < NORMED_K_HELD; ++i) {
+      const int c = tid + i * threads;
+      if (c < k_size) write_k(c, k[i]);
+    }
+  } else {
+#pragma unroll 4
+    for (int c = tid; c < q_size; c += threads)
+      write_q(c, in[c] + (a.q_bias != nullptr ? a.q_bias[c] : 0.0f));
+#pragma unroll 4
+    for (int c = tid; c < k_size; c += threads)
+      write_k(c, k_in[c] + (a.k_bias != nullptr ? a.k_bias[c] : 0.0f));
+  }
+  // ---- values, kept for or blended with another layer's
   float* source = a.value_source == nullptr ? nullptr
                                             : a.value_source + static_cast<size_t>(token) * v_size;
-  for (int head = warp; head < a.kv_heads; head += warps)
 #pragma unroll 4
-  for (int d = lane; d < R; d += 32) {
-    const int c = head * R + d;
-    float k = 0.0f, v = 0.0f;
-    if (d < D) {
-      const int i = head * D + d;
-      k = biased(i, a.k_bias, q_size) * k_inverse;
-      if (a.k_weight != nullptr) k *= a.k_weight[i];
+  for (int c = tid; c < v_size; c += threads) {
+    float v = v_in[c] + (a.v_bias != nullptr ? a.v_bias[c] : 0.0f);
+    if (a.value_mix == 1) {
+      source[c] = v;
+    } else if (a.value_mix == 2) {
+      v = (1.0f - a.lambda) * v + a.lambda * source[c];
     }
-    if (d < E) {
-      const int i = head * E + d;
-      v = biased(i, a.v_bias, q_size + k_size);
-      if (a.value_mix == 1) {
-        source[i] = v;
-      } else if (a.value_mix == 2) {
-        v = (1.0f - a.lambda) * v + a.lambda * source[i];
+    const int head = by_value_dim.quotient(c);
+    put(a.v_cache, value_rows, head, c - head * E, v);
+  }
+  // ---- zeros behind a head's own coordinates
+  if (R > D) {
+    const int pad = R - D;
+    for (int p = tid; p < (a.heads + a.kv_heads) * pad; p += threads) {
+      const int head = p / pad, d = D + p - head * pad;
+      if (head < a.heads) {
+        out[head * R + d] = hx_from_float<T>(0.0f);
+      } else {
+        put(a.k_cache, key_rows, head - a.heads, d, 0.0f);
       }
     }
-    if (!append) {
-      keys[c] = hx_from_float<T>(k);
-      values[c] = hx_from_float<T>(v);
-    } else if (page >= 0) {
-      const size_t at = hx_cache_offset(page, head, slot, d, a.kv_heads, a.page_size, R, chunk);
-      a.k_cache[at] = hx_from_float<T>(k);
-      a.v_cache[at] = hx_from_float<T>(v);
+  }
+  if (R > E) {
+    const int pad = R - E;
+    for (int p = tid; p < a.kv_heads * pad; p += threads) {
+      const int head = p / pad;
+      put(a.v_cache, value_rows, head, E + p - head * pad, 0.0f);
     }
   }
   if (a.gates != nullptr)
-    for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
+    for (int h = tid; h < a.heads; h += threads)
       a.gates[static_cast<size_t>(token) * a.heads + h] =
           hx_sigmoid(in[q_size + k_size + v_size + h]);
   if (a.clear) {
     __syncthreads();
     const int used = q_size + k_size + v_size + (a.gates != nullptr ? a.heads : 0);
-    for (int c = threadIdx.x; c < used; c += blockDim.x) in[c] = 0.0f;
+    for (int c = tid; c < used; c += threads) in[c] = 0.0f;
   }
 }
 
-// grid (tokens): a warp takes a head at a time
+// grid (tokens, ceil(heads / 8)): a warp takes a head
+constexpr int HEAD_GATE_WARPS = 8;
+
 template <typename T>
-__global__ __launch_bounds__(256) void head_gate_kernel(T* __restrict__ context, int ld_context,
-                                                        const float* __restrict__ gates,
-                                                        int heads, int row_dim) {
+__global__ __launch_bounds__(HEAD_GATE_WARPS * 32) void head_gate_kernel(
+    T* __restrict__ context, int ld_context, const float* __restrict__ gates, int heads,
+    int row_dim) {
   hx_pdl_prologue();
   const int token = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  T* row = context + static_cast<size_t>(token) * ld_context;
-  for (int head = warp; head < heads; head += warps) {
-    const float gate = gates[static_cast<size_t>(token) * heads + head];
+  const int head = blockIdx.y * HEAD_GATE_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (head >= heads) return;
+  const float gate = gates[static_cast<size_t>(token) * heads + head];
+  T* row = context + static_cast<size_t>(token) * ld_context + head * row_dim;
 #pragma unroll 4
-    for (int c = lane; c < row_dim; c += 32)
-      row[head * row_dim + c] = hx_from_float<T>(hx_to_float<T>(row[head * row_dim + c]) * gate);
-  }
+  for (int c = lane; c < row_dim; c += 32) row[c] = hx_from_float<T>(hx_to_float<T>(row[c]) * gate);
 }
 
 // grid (tokens)
@@ -335,7 +400,10 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                  ((q_weight == nullptr && k_weight == nullptr) || eps > 0.0f),
              "hx_biased_normed_rows: bad constants");
   if (tokens == 0) return HX_OK;
-  const int threads = tokens <= NORMED_ROWS_FEW_TOKENS ? 1024 : 256;
+  HX_REQUIRE(static_cast<long long>(heads) * head_dim < 65536 &&
+                 static_cast<long long>(kv_heads) * value_dim < 65536 && row_dim < 65536,
+             "hx_biased_normed_rows: projections of 65,536 numbers and more are not supported");
+  const FastDivisor by_dim = fast_divisor(head_dim), by_value_dim = fast_divisor(value_dim);
   if (dtype == HX_F32) {
     NormedRowsArgs<float> a{projected, ld_projected, clear, q_bias, k_bias, v_bias, q_weight,
                             k_weight, eps, positions, temp_coef, temp_every, value_mix, lambda,
@@ -344,7 +412,8 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                             request_table_row, block_tables, table_stride,
                             static_cast<float*>(k_cache), static_cast<float*>(v_cache), page_size,
                             num_pages, status};
-    hx_launch(biased_normed_rows_kernel<float>, dim3(tokens), threads, 0, stream, a);
+    hx_launch(biased_normed_rows_kernel<float>, dim3(tokens), NORMED_ROWS_THREADS, 0, stream, a,
+              by_dim, by_value_dim);
   } else if (dtype == HX_BF16) {
     NormedRowsArgs<__nv_bfloat16> a{projected, ld_projected, clear, q_bias, k_bias, v_bias,
                                     q_weight, k_weight, eps, positions, temp_coef, temp_every,
@@ -355,7 +424,8 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                                     static_cast<__nv_bfloat16*>(k_cache),
                                     static_cast<__nv_bfloat16*>(v_cache), page_size, num_pages,
                                     status};
-    hx_launch(biased_normed_rows_kernel<__nv_bfloat16>, dim3(tokens), threads, 0, stream, a);
+    hx_launch(biased_normed_rows_kernel<__nv_bfloat16>, dim3(tokens), NORMED_ROWS_THREADS, 0,
+              stream, a, by_dim, by_value_dim);
   } else {
     HX_REQUIRE(false, "hx_biased_normed_rows: unknown dtype %d", dtype);
   }
@@ -366,14 +436,15 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
 // context[t][h * row_dim + c] *= gates[t][h]; context in `dtype`, gates float32 [tokens, heads].
 HX_API int hx_head_gate(void* context, int ld_context, const float* gates, int dtype, int tokens,
                         int heads, int row_dim, cudaStream_t stream) {
-  HX_REQUIRE(tokens >= 0 && heads > 0 && row_dim > 0 &&
+  HX_REQUIRE(tokens >= 0 && heads > 0 && heads <= 65535 * HEAD_GATE_WARPS && row_dim > 0 &&
                  ld_context >= heads * row_dim, "hx_head_gate: bad sizes");
   if (tokens == 0) return HX_OK;
+  const dim3 grid(tokens, (heads + HEAD_GATE_WARPS - 1) / HEAD_GATE_WARPS);
   if (dtype == HX_F32) {
-    hx_launch(head_gate_kernel<float>, dim3(tokens), 256, 0, stream,
+    hx_launch(head_gate_kernel<float>, grid, HEAD_GATE_WARPS * 32, 0, stream,
               static_cast<float*>(context), ld_context, gates, heads, row_dim);
   } else if (dtype == HX_BF16) {
-    hx_launch(head_gate_kernel<__nv_bfloat16>, dim3(tokens), 256, 0, stream,
+    hx_launch(head_gate_kernel<__nv_bfloat16>, grid, HEAD_GATE_WARPS * 32, 0, stream,
               static_cast<__nv_bfloat16*>(context), ld_context, gates, heads, row_dim);
   } else {
     HX_REQUIRE(false, "hx_head_gate: unknown dtype %d", dtype);
