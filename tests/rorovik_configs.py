@@ -79,11 +79,11 @@ CONFIGS = {
     "fast": {
         "architecture": "Rorovik", "vocab": 512, "width": 256, "norm": {"eps": 1e-5},
         "residual_mult": 0.5, "token_side": {"dim": 16},
-        "layers": [_attention(4, 2, 64, 64, 44, (0.3, 64), True, _moe(128, 1.5, 8, 2, 2),
+        "layers": [_attention(4, 2, 64, 64, 44, (0.25, 64), True, _moe(128, 1.25, 8, 2, 2),
                               sharp=6.0),
-                   _latent(4, 64, 32, 64, 96, 128, 500000.0, (8.0, 128, 32.0, 1.0),
+                   _latent(4, 64, 48, 64, 80, 96, 500000.0, (6.0, 128, 16.0, 2.0),
                            _dense(256), sharp=6.0),
-                   _attention(4, 1, 64, 128, None, (0.3, 100), True, _moe(128, 1.5, 4, 4, 2),
+                   _attention(4, 1, 64, 128, None, (0.4, 100), True, _moe(128, 2.5, 4, 4, 2),
                               sharp=4.0)],
     },
     "odd": {
