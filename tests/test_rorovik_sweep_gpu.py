@@ -82,9 +82,9 @@ def draw_config(seed: int):
               "norm": {"eps": float(pick([1e-6, 1e-5, 1e-3]))},
               "residual_mult": float(pick([1.0, 0.3, 0.7, -0.5])), "layers": layers}
     if rng.random() < 0.8:
-        # (a token input of one or two numbers is normed to little more than its sign: whatever
-        # rounds differently near zero flips it, in any implementation)
-        config["token_side"] = {"dim": pick([4, 8, 16, 40])}
+        # (a token input of a few numbers is normed to little more than their signs: where all of
+        # its gates are near zero, whatever rounds differently turns it, in any implementation)
+        config["token_side"] = {"dim": pick([8, 16, 24, 40])}
     return config
 
 
