@@ -304,6 +304,180 @@ __global__ __launch_bounds__(NORMED_ROWS_THREADS) void biased_normed_rows_kernel
   }
 }
 
+// The same four numbers at a time, for projections whose heads, rows and strides are multiples of
+// four and whose buffers are 16-byte aligned (the host checks): a load, a bias, a weight and a
+// store serve four numbers, and their head is worked out once.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+  return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+__device__ __forceinline__ float4 scale4(float4 a, float4 w, float f) {
+  return make_float4(a.x * w.x * f, a.y * w.y * f, a.z * w.z * f, a.w * w.w * f);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  uint2 packed;
+  *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = packed;
+}
+
+template <typename T>
+__global__ __launch_bounds__(NORMED_ROWS_THREADS) void biased_normed_rows_quads_kernel(
+    const NormedRowsArgs<T> a, const FastDivisor by_dim, const FastDivisor by_value_dim) {
+  constexpr int Q_QUADS = NORMED_Q_HELD / 4, K_QUADS = NORMED_K_HELD / 4;
+  __shared__ float scratch[32];
+  hx_pdl_prologue();
+  const int token = blockIdx.x;
+  const int tid = threadIdx.x, threads = blockDim.x;
+  float* in = a.projected + static_cast<size_t>(token) * a.ld_projected;
+  T* out = a.rows + static_cast<size_t>(token) * a.ld_rows;
+  const int D = a.head_dim, R = a.row_dim, E = a.value_dim;
+  const int q_size = a.heads * D;
+  const int k_size = a.kv_heads * D;
+  const int v_size = a.kv_heads * E;
+  float* k_in = in + q_size;
+  float* v_in = k_in + k_size;
+  const bool held = q_size <= NORMED_Q_HELD * threads && k_size <= NORMED_K_HELD * threads;
+  const float4 ones = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+
+  // where keys and values go (see biased_normed_rows_kernel)
+  const bool append = a.k_cache != nullptr;
+  int page = -1, slot = 0;
+  if (append) {
+    const int position = a.positions[token];
+    const int table_row = a.request_table_row[a.token_request[token]];
+    page = a.block_tables[static_cast<size_t>(table_row) * a.table_stride + position / a.page_size];
+    slot = position % a.page_size;
+    if (page < 0 || page >= a.num_pages) {
+      if (tid == 0 && a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
+      page = -1;
+    }
+  }
+  auto biased_q = [&](int c) {
+    const float4 v = load4(in + c);
+    return a.q_bias != nullptr ? add4(v, load4(a.q_bias + c)) : v;
+  };
+  auto biased_k = [&](int c) {
+    const float4 v = load4(k_in + c);
+    return a.k_bias != nullptr ? add4(v, load4(a.k_bias + c)) : v;
+  };
+  auto squares = [](float4 v, float sum) {
+    sum = fmaf(v.x, v.x, sum); sum = fmaf(v.y, v.y, sum);
+    sum = fmaf(v.z, v.z, sum); return fmaf(v.w, v.w, sum);
+  };
+  float4 q[Q_QUADS], k[K_QUADS];
+  float q_sum = 0.0f, k_sum = 0.0f;
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < Q_QUADS; ++i) {
+      const int c = 4 * (tid + i * threads);
+      q[i] = c < q_size ? biased_q(c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+#pragma unroll
+    for (int i = 0; i < K_QUADS; ++i) {
+      const int c = 4 * (tid + i * threads);
+      k[i] = c < k_size ? biased_k(c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+#pragma unroll
+    for (int i = 0; i < Q_QUADS; ++i) q_sum = squares(q[i], q_sum);
+#pragma unroll
+    for (int i = 0; i < K_QUADS; ++i) k_sum = squares(k[i], k_sum);
+  } else {
+    for (int c = 4 * tid; c < q_size; c += 4 * threads) q_sum = squares(biased_q(c), q_sum);
+    for (int c = 4 * tid; c < k_size; c += 4 * threads) k_sum = squares(biased_k(c), k_sum);
+  }
+  float q_factor = 1.0f, k_factor = 1.0f;
+  if (a.q_weight != nullptr)
+    q_factor = 1.0f / sqrtf(hx_block_sum(q_sum, scratch) / static_cast<float>(q_size) + a.eps);
+  if (a.k_weight != nullptr)
+    k_factor = 1.0f / sqrtf(hx_block_sum(k_sum, scratch) / static_cast<float>(k_size) + a.eps);
+  if (a.temp_every > 0)
+    q_factor *= 1.0f + a.temp_coef *
+        logf(static_cast<float>((a.positions[token] + 1) / a.temp_every) + 1.0f);
+
+  const int chunk = hx_cache_chunk(sizeof(T), R);      // a multiple of four here
+  T* key_rows = out + a.heads * R;
+  T* value_rows = key_rows + a.kv_heads * R;
+  auto put4 = [&](T* cache, T* rows, int head, int d, float4 value) {
+    if (!append) {
+      store4(rows + head * R + d, value);
+    } else if (page >= 0) {
+      store4(cache + hx_cache_offset(page, head, slot, d, a.kv_heads, a.page_size, R, chunk), value);
+    }
+  };
+  auto write_q = [&](int c, float4 value) {
+    const int head = by_dim.quotient(c);
+    store4(out + head * R + (c - head * D),
+           scale4(value, a.q_weight != nullptr ? load4(a.q_weight + c) : ones, q_factor));
+  };
+  auto write_k = [&](int c, float4 value) {
+    const int head = by_dim.quotient(c);
+    put4(a.k_cache, key_rows, head, c - head * D,
+         scale4(value, a.k_weight != nullptr ? load4(a.k_weight + c) : ones, k_factor));
+  };
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < Q_QUADS; ++i) {
+      const int c = 4 * (tid + i * threads);
+      if (c < q_size) write_q(c, q[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < K_QUADS; ++i) {
+      const int c = 4 * (tid + i * threads);
+      if (c < k_size) write_k(c, k[i]);
+    }
+  } else {
+    for (int c = 4 * tid; c < q_size; c += 4 * threads) write_q(c, biased_q(c));
+    for (int c = 4 * tid; c < k_size; c += 4 * threads) write_k(c, biased_k(c));
+  }
+  float* source = a.value_source == nullptr ? nullptr
+                                            : a.value_source + static_cast<size_t>(token) * v_size;
+  for (int c = 4 * tid; c < v_size; c += 4 * threads) {
+    float4 v = load4(v_in + c);
+    if (a.v_bias != nullptr) v = add4(v, load4(a.v_bias + c));
+    if (a.value_mix == 1) {
+      store4(source + c, v);
+    } else if (a.value_mix == 2) {
+      const float4 s = load4(source + c);
+      const float keep = 1.0f - a.lambda;
+      v = make_float4(keep * v.x + a.lambda * s.x, keep * v.y + a.lambda * s.y,
+                      keep * v.z + a.lambda * s.z, keep * v.w + a.lambda * s.w);
+    }
+    const int head = by_value_dim.quotient(c);
+    put4(a.v_cache, value_rows, head, c - head * E, v);
+  }
+  // zeros behind a head's own coordinates, four at a time
+  const float4 zeros = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (R > D) {
+    const int pad = (R - D) >> 2;
+    for (int p = tid; p < (a.heads + a.kv_heads) * pad; p += threads) {
+      const int head = p / pad, d = D + 4 * (p - head * pad);
+      if (head < a.heads) {
+        store4(out + head * R + d, zeros);
+      } else {
+        put4(a.k_cache, key_rows, head - a.heads, d, zeros);
+      }
+    }
+  }
+  if (R > E) {
+    const int pad = (R - E) >> 2;
+    for (int p = tid; p < a.kv_heads * pad; p += threads) {
+      const int head = p / pad;
+      put4(a.v_cache, value_rows, head, E + 4 * (p - head * pad), zeros);
+    }
+  }
+  if (a.gates != nullptr)
+    for (int h = tid; h < a.heads; h += threads)
+      a.gates[static_cast<size_t>(token) * a.heads + h] =
+          hx_sigmoid(in[q_size + k_size + v_size + h]);
+  if (a.clear) {
+    __syncthreads();
+    const int used = q_size + k_size + v_size + (a.gates != nullptr ? a.heads : 0);
+    for (int c = tid; c < used; c += threads) in[c] = 0.0f;
+  }
+}
+
 // grid (tokens, ceil(heads / 8)): a warp takes a head
 constexpr int HEAD_GATE_WARPS = 8;
 
@@ -404,6 +578,17 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                  static_cast<long long>(kv_heads) * value_dim < 65536 && row_dim < 65536,
              "hx_biased_normed_rows: projections of 65,536 numbers and more are not supported");
   const FastDivisor by_dim = fast_divisor(head_dim), by_value_dim = fast_divisor(value_dim);
+  // four numbers at a time where every piece starts on a 16-byte boundary (8 for bfloat16 rows)
+  auto aligned = [](const void* p, uintptr_t to) {
+    return p == nullptr || (reinterpret_cast<uintptr_t>(p) & (to - 1)) == 0;
+  };
+  const uintptr_t row_bytes = dtype == HX_F32 ? 16 : 8;
+  const bool quads =
+      head_dim % 4 == 0 && value_dim % 4 == 0 && row_dim % 4 == 0 && ld_projected % 4 == 0 &&
+      ld_rows % 4 == 0 && aligned(projected, 16) && aligned(q_bias, 16) && aligned(k_bias, 16) &&
+      aligned(v_bias, 16) && aligned(q_weight, 16) && aligned(k_weight, 16) &&
+      aligned(value_source, 16) && aligned(rows, row_bytes) && aligned(k_cache, 16) &&
+      aligned(v_cache, 16);
   if (dtype == HX_F32) {
     NormedRowsArgs<float> a{projected, ld_projected, clear, q_bias, k_bias, v_bias, q_weight,
                             k_weight, eps, positions, temp_coef, temp_every, value_mix, lambda,
@@ -412,8 +597,8 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                             request_table_row, block_tables, table_stride,
                             static_cast<float*>(k_cache), static_cast<float*>(v_cache), page_size,
                             num_pages, status};
-    hx_launch(biased_normed_rows_kernel<float>, dim3(tokens), NORMED_ROWS_THREADS, 0, stream, a,
-              by_dim, by_value_dim);
+    hx_launch(quads ? biased_normed_rows_quads_kernel<float> : biased_normed_rows_kernel<float>,
+              dim3(tokens), NORMED_ROWS_THREADS, 0, stream, a, by_dim, by_value_dim);
   } else if (dtype == HX_BF16) {
     NormedRowsArgs<__nv_bfloat16> a{projected, ld_projected, clear, q_bias, k_bias, v_bias,
                                     q_weight, k_weight, eps, positions, temp_coef, temp_every,
@@ -424,8 +609,9 @@ HX_API int hx_biased_normed_rows(float* projected, int ld_projected, int clear,
                                     static_cast<__nv_bfloat16*>(k_cache),
                                     static_cast<__nv_bfloat16*>(v_cache), page_size, num_pages,
                                     status};
-    hx_launch(biased_normed_rows_kernel<__nv_bfloat16>, dim3(tokens), NORMED_ROWS_THREADS, 0,
-              stream, a, by_dim, by_value_dim);
+    hx_launch(quads ? biased_normed_rows_quads_kernel<__nv_bfloat16>
+                    : biased_normed_rows_kernel<__nv_bfloat16>,
+              dim3(tokens), NORMED_ROWS_THREADS, 0, stream, a, by_dim, by_value_dim);
   } else {
     HX_REQUIRE(false, "hx_biased_normed_rows: unknown dtype %d", dtype);
   }
