@@ -65,8 +65,12 @@ __device__ __forceinline__ void load_weight_box(void* dst, const CUtensorMap* ma
 template <int BN, int EPI>
 __device__ __forceinline__ void write_tile(void* out, int ldo, int tokens, int features,
                                            uint32_t lane_address, int feature, int token0,
-                                           int activation, float gate_limit) {
+                                           int activation, float gate_limit,
+                                           const float* gate_bias, const float* up_bias) {
   const bool feature_ok = feature < features;
+  // this thread's feature is one row of the gate and one of the up matrix: one bias each
+  const float gate_b = EPI == EPI_SWIGLU && gate_bias != nullptr && feature_ok ? gate_bias[feature] : 0.0f;
+  const float up_b = EPI == EPI_SWIGLU && up_bias != nullptr && feature_ok ? up_bias[feature] : 0.0f;
 #pragma unroll 1
   for (int column = 0; column < BN; column += 16) {
     if (token0 + column >= tokens) break;   // uniform over the warp
@@ -76,7 +80,8 @@ __device__ __forceinline__ void write_tile(void* out, int ldo, int tokens, int f
       float up[16];
       tmem_load16(lane_address + BN + column, up);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] = hx_gated_fast(acc[j], up[j], activation, gate_limit);
+      for (int j = 0; j < 16; ++j)
+        acc[j] = hx_gated_fast(acc[j] + gate_b, up[j] + up_b, activation, gate_limit);
     }
     if (feature_ok) {
 #pragma unroll
@@ -140,6 +145,9 @@ struct GemmArgs {
   const int* tile_group = nullptr;
   int group_rows = 0;
   float gate_limit = 0.0f;    // gated epilogue: the limit of HX_GATE_CLAMPED_SIGMOID
+  // gated epilogue: float32 biases of the gate and the up rows, [features] each (null: none)
+  const float* gate_bias = nullptr;
+  const float* up_bias = nullptr;
 };
 
 template <int BN, int EPI>
@@ -276,7 +284,7 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
         tc_fence_after();
         const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         write_tile<BN, EPI>(args.out, args.ldo, args.tokens, args.features, lane_address, feature,
-                            token0, args.activation, args.gate_limit);
+                            token0, args.activation, args.gate_limit, args.gate_bias, args.up_bias);
       }
     }
   }
@@ -371,6 +379,9 @@ struct PersistentArgs {
   const int* tile_group;
   int group_rows;
   float gate_limit = 0.0f;    // gated epilogue: the limit of HX_GATE_CLAMPED_SIGMOID
+  // gated epilogue: float32 biases of the gate and the up rows, [features] each (null: none)
+  const float* gate_bias = nullptr;
+  const float* up_bias = nullptr;
 };
 
 // What a CTA works on at a time: a tile, or (`partial`) a run of k-blocks of a tile that
@@ -452,7 +463,8 @@ __device__ __forceinline__ void load_row_into_accumulator(const float* out, int 
 template <int EPI>
 __device__ __forceinline__ void write_row(void* out, int ldo, int features, uint32_t lane_address,
                                           int token, int tokens, int feature0, int activation,
-                                          float gate_limit) {
+                                          float gate_limit, const float* gate_bias,
+                                          const float* up_bias) {
   using Element = typename std::conditional<EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU,
                                             __nv_bfloat16, float>::type;
   constexpr int kColumns = EPI == EPI_SWIGLU ? BM : 2 * BM;
@@ -466,6 +478,17 @@ __device__ __forceinline__ void write_row(void* out, int ldo, int features, uint
     if (EPI == EPI_SWIGLU) {
       float up[16];
       tmem_load16(lane_address + BM + column, up);
+      if (gate_bias != nullptr || up_bias != nullptr) {
+        // this thread's 16 features: their biases (the same for every token of the tile)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int feature = feature0 + column + j;
+          if (feature < features) {
+            if (gate_bias != nullptr) acc[j] += gate_bias[feature];
+            if (up_bias != nullptr) up[j] += up_bias[feature];
+          }
+        }
+      }
 #pragma unroll
       for (int j = 0; j < 16; ++j) acc[j] = hx_gated_fast(acc[j], up[j], activation, gate_limit);
     }
@@ -790,7 +813,8 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
         write_row<EPI>(args.out, args.ldo, args.features,
                        lane_base + buffer * Config::kBufferColumns,
                        unit.token_tile * BM + quarter * 32 + lane, args.tokens,
-                       unit.feature_tile * FEATURES, args.activation, args.gate_limit);
+                       unit.feature_tile * FEATURES, args.activation, args.gate_limit,
+                       args.gate_bias, args.up_bias);
       }
       // every lane's tcgen05.ld has completed (the loads are waited for where they are
       // issued): hand the accumulator back
@@ -1013,17 +1037,12 @@ HX_API int hx_gemm_tc_supports(int tokens, int features, int depth, int ldx, int
 // [128][64] elements, zero padded (ldw is ignored; up_row_offset is then a multiple of 128).
 // x_capacity_rows: rows of the buffer behind x (the tensor map is made for the buffer, so it
 // can be reused for every batch size).
-HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
-                      int weight_rows, void* out, int ldo, int tokens, int features, int depth,
-                      int epilogue, int up_row_offset, int k_splits, int weight_tiles, int* status,
-                      cudaStream_t stream) {
+static int gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                   int weight_rows, void* out, int ldo, int tokens, int features, int depth,
+                   int epilogue, int activation, float gate_limit, const float* gate_bias,
+                   const float* up_bias, int up_row_offset, int k_splits, int weight_tiles,
+                   int* status, cudaStream_t stream) {
   if (weight_tiles) ldw = 8;      // not a stride of anything here
-  // the gated epilogue by the gate's activation: 3 is silu(gate) * up, 5 gelu_tanh(gate) * up
-  int activation = HX_GATE_SILU;
-  if (epilogue == 5) {
-    epilogue = EPI_SWIGLU;
-    activation = HX_GATE_GELU_TANH;
-  }
   HX_REQUIRE(!weight_tiles || epilogue != EPI_SWIGLU || up_row_offset % BM == 0,
              "hx_gemm_tc: with tiled weights the up rows must start on a multiple of %d", BM);
   HX_REQUIRE(hx_gemm_tc_supports(tokens, features, depth, ldx, ldw),
@@ -1064,7 +1083,8 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
 
   if (persistent) {
     PersistentArgs args{out, ldo, tokens, features, depth, up_row_offset, k_tiles, 0, 0,
-                        total_k_blocks, status, RopeArgs{}, -1, activation};
+                        total_k_blocks, status, RopeArgs{}, -1, activation, nullptr, 0,
+                        gate_limit, gate_bias, up_bias};
     rc = launch_persistent_epilogue(epilogue, map_w, map_x, args, stream);
     if (rc != HX_OK) return rc;
     HX_CHECK_LAUNCH("hx_gemm_tc");
@@ -1074,7 +1094,7 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
   const int per_split = (total_k_blocks + k_splits - 1) / k_splits;
   k_splits = (total_k_blocks + per_split - 1) / per_split;
   GemmArgs args{out, ldo, tokens, features, depth, up_row_offset, per_split, k_tiles, status,
-                activation};
+                activation, nullptr, 0, gate_limit, gate_bias, up_bias};
   const dim3 grid((tokens + bn - 1) / bn, (features + BM - 1) / BM, k_splits);
   HX_REQUIRE(grid.y <= 65535, "hx_gemm_tc: too many features (%d)", features);
 
@@ -1088,6 +1108,36 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_gemm_tc");
   return HX_OK;
+}
+
+HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                      int weight_rows, void* out, int ldo, int tokens, int features, int depth,
+                      int epilogue, int up_row_offset, int k_splits, int weight_tiles, int* status,
+                      cudaStream_t stream) {
+  // the gated epilogue by the gate's activation: 3 is silu(gate) * up, 5 gelu_tanh(gate) * up
+  int activation = HX_GATE_SILU;
+  if (epilogue == 5) {
+    epilogue = EPI_SWIGLU;
+    activation = HX_GATE_GELU_TANH;
+  }
+  return gemm_tc(x, ldx, x_capacity_rows, w, ldw, weight_rows, out, ldo, tokens, features, depth,
+                 epilogue, activation, 0.0f, nullptr, nullptr, up_row_offset, k_splits,
+                 weight_tiles, status, stream);
+}
+
+// The product with the gated epilogue for every HxGateActivation and with float32 biases on
+// the gate and the up rows ([features] each, either may be null): out = f(gate + gate_bias,
+// up + up_bias) in the compute type.
+HX_API int hx_gemm_tc_gated(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                            int weight_rows, void* out, int ldo, int tokens, int features,
+                            int depth, int activation, float gate_limit, const float* gate_bias,
+                            const float* up_bias, int up_row_offset, int weight_tiles,
+                            int* status, cudaStream_t stream) {
+  HX_REQUIRE(activation >= HX_GATE_SILU && activation <= HX_GATE_CLAMPED_SIGMOID,
+             "hx_gemm_tc_gated: unknown activation %d", activation);
+  return gemm_tc(x, ldx, x_capacity_rows, w, ldw, weight_rows, out, ldo, tokens, features, depth,
+                 EPI_SWIGLU, activation, gate_limit, gate_bias, up_bias, up_row_offset, 1,
+                 weight_tiles, status, stream);
 }
 
 // The grouped product: rows of x come in tiles of `token_tile` (16, 32, 64, 128 or 256), and

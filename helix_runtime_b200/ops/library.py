@@ -85,6 +85,10 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_gemm_tc.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_int,
                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                                    _c_ptr]
+    library.hx_gemm_tc_gated.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr,
+                                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr,
+                                         _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr]
+    library.hx_gemm_tc_gated.restype = _c_int
     library.hx_gemm_tc_rope_append.argtypes = [
         _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
         _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
@@ -508,10 +512,14 @@ def tile_weights(matrix: torch.Tensor) -> torch.Tensor:
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tokens: int, features: int,
             epilogue: int, status: torch.Tensor, up_row_offset: int = 0, k_splits: int = 1,
-            weight_shape: Optional[Tuple[int, int]] = None) -> None:
+            weight_shape: Optional[Tuple[int, int]] = None, gate_activation: Optional[int] = None,
+            gate_limit: float = 0.0, gate_bias: Optional[torch.Tensor] = None,
+            up_bias: Optional[torch.Tensor] = None) -> None:
     """out[:tokens, :features] (op)= x[:tokens] @ w.T on the tensor cores (bfloat16).  ``w``
     is the matrix ``[rows, depth]`` or its tiles from :func:`tile_weights` (then
-    ``weight_shape`` gives rows and depth)."""
+    ``weight_shape`` gives rows and depth).  With ``gate_activation`` (any of GATE_ACTIVATIONS)
+    the epilogue is that gated activation of ``[gate; up]`` whatever ``epilogue`` says, with the
+    optional float32 biases ``gate_bias`` and ``up_bias`` ``[features]`` added first."""
     _need(x, torch.bfloat16, "x")
     _need(w, torch.bfloat16, "w")
     tiled = w.dim() == 4
@@ -526,6 +534,17 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tokens: int, fe
     else:
         rows, depth = w.shape
         ldw = w.stride(0)
+    if gate_activation is not None:
+        for bias in (gate_bias, up_bias):
+            if bias is not None:
+                _need(bias, torch.float32, "bias")
+                assert bias.numel() == features and bias.is_contiguous()
+        _check(lib().hx_gemm_tc_gated(x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), ldw,
+                                      rows, out.data_ptr(), out.stride(0), tokens, features, depth,
+                                      int(gate_activation), float(gate_limit), _ptr(gate_bias),
+                                      _ptr(up_bias), up_row_offset, 1 if tiled else 0,
+                                      status.data_ptr(), _stream()))
+        return
     _check(lib().hx_gemm_tc(x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), ldw, rows,
                             out.data_ptr(), out.stride(0), tokens, features, depth, epilogue,
                             up_row_offset, k_splits, 1 if tiled else 0, status.data_ptr(),

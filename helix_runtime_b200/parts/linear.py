@@ -162,10 +162,16 @@ def project_gated(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: to
                   ordered: bool, activation: int, gate_bias: Optional[torch.Tensor] = None,
                   up_bias: Optional[torch.Tensor] = None, limit: float = 0.0) -> None:
     """``act[:tokens] = f(x @ gate.T + gate_bias, x @ up.T + up_bias)`` for any of
-    ``ops.GATE_ACTIVATIONS``, biases optional: the product leaves float32 sums (a split-K weight
-    stream for few tokens, else the tensor-core or CUDA-core product with a float32 store) and
-    one kernel adds the biases, applies the gate and rounds once."""
+    ``ops.GATE_ACTIVATIONS``, biases optional.  Many tokens on the tensor cores: biases and gate
+    are the product's epilogue.  Otherwise the product leaves float32 sums (a split-K weight
+    stream for few tokens, else the CUDA-core product) and one kernel adds the biases, applies
+    the gate and rounds once."""
     if tokens == 0:
+        return
+    if uses_tensor_cores(x, w_gate_up, tokens) and not is_weight_stream(x, w_gate_up, tokens):
+        _gemm_tc(x, w_gate_up, act, tokens, intermediate, ops.EPI_SWIGLU, status,
+                 up_row_offset=intermediate, gate_activation=activation, gate_limit=limit,
+                 gate_bias=gate_bias, up_bias=up_bias)
         return
     if is_weight_stream(x, w_gate_up, tokens):
         sums = workspace.accumulator(f"mlp.gate_up/{intermediate}",

@@ -358,6 +358,12 @@ int hx_gemm_tc_rope_append(const void* x, int ldx, int x_capacity_rows, const vo
                            int head_dim, int rotary_dim, int page_size, int num_pages, int* status,
                            cudaStream_t stream);
 
+/* hx_gemm_tc with the gated epilogue for every gate activation (see hx_biased_gated_activation)
+ * and float32 biases on the gate and the up rows ([features] each, either may be null) */
+int hx_gemm_tc_gated(const void* x, int ldx, int x_capacity_rows, const void* w, int ldw,
+                     int weight_rows, void* out, int ldo, int tokens, int features, int depth,
+                     int activation, float gate_limit, const float* gate_bias, const float* up_bias,
+                     int up_row_offset, int weight_tiles, int* status, cudaStream_t stream);
 /* grouped product: rows of x come in tiles of token_tile (16..256), tile t multiplies with
  * group tile_group[t] of w (`groups` matrices of group_rows rows one below the other); a
  * negative entry skips the tile; tile_group is device memory, written on the stream before */

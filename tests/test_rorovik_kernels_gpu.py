@@ -504,6 +504,38 @@ def test_gate_and_up_with_biases_through_relu(dtype):
     assert (as_double(buffer) == 0).all()
 
 
+@pytest.mark.parametrize("tokens,width,ff,tiled", [(200, 64, 136, False), (300, 128, 256, True),
+                                                   (2100, 256, 384, True), (129, 72, 40, False)])
+@pytest.mark.parametrize("activation,limit", [("relu", 0.0), ("clamped_sigmoid", 0.9), ("silu", 0.0)])
+def test_biases_and_gate_as_the_epilogue_of_the_product(tokens, width, ff, tiled, activation, limit):
+    """Prompt portions on the tensor cores: ``f(x Wg' + bg, x Wu' + bu)`` leaves the product's
+    epilogue in bfloat16, with the weights row-major and as tiles."""
+    from helix_runtime_b200.ops import library as ops
+    rng = np.random.default_rng(tokens + ff)
+    x = held(rng.normal(size=(tokens, width)), torch.bfloat16)
+    w = held(rng.normal(size=(2 * ff, width)) * 1.5 / math.sqrt(width), torch.bfloat16)
+    gate_bias, up_bias = (held(rng.normal(size=ff) * 0.5, torch.float32) for _ in range(2))
+    gate, up = x @ w[:ff].T + gate_bias, x @ w[ff:].T + up_bias
+    if activation == "relu":
+        want = np.maximum(gate, 0.0) * up
+    elif activation == "silu":
+        want = gate * plain.sigmoid(gate) * up
+    else:
+        g, u = np.minimum(gate, limit), np.clip(up, -limit, limit)
+        want = g * plain.sigmoid(1.702 * g) * (u + 1.0)
+    out = torch.full((tokens + 3, ff), 9.0, dtype=torch.bfloat16, device="cuda")
+    status = status_word()
+    matrix = device_tensor(w, torch.bfloat16)
+    held_w = ops.tile_weights(matrix) if tiled else matrix
+    ops.gemm_tc(device_tensor(x, torch.bfloat16), held_w, out, tokens, ff, ops.EPI_SWIGLU, status,
+                up_row_offset=ff, weight_shape=(2 * ff, width) if tiled else None,
+                gate_activation=ops.GATE_ACTIVATIONS[activation], gate_limit=limit,
+                gate_bias=device_tensor(gate_bias), up_bias=device_tensor(up_bias))
+    assert int(status.item()) == 0
+    close(as_double(out)[:tokens], want, 2e-2, 1e-2, what=f"{activation} of {tokens} tokens")
+    assert (as_double(out)[tokens:] == 9.0).all()
+
+
 # ------------------------------------------------------------- stretched rotary frequencies
 
 @pytest.mark.parametrize("dims,base,scaling", [
